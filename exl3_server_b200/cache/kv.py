@@ -57,7 +57,10 @@ class KVGroup:
         # one page more than the pool hands out: rows that only pad a batch write there
         shape = (len(self.owners), self.pool.n_pages + 1, r.kv_heads, self.page_size)
         self.k, self._k_store = self._guarded(shape + (r.head_dim,), dtype, device)
-        self.v, self._v_store = self._guarded(shape + (r.value_dim or r.head_dim,), dtype, device)
+        if r.values_in_keys:
+            self.v = self.k                # the mixer reads its values out of the rows it keeps as keys
+        else:
+            self.v, self._v_store = self._guarded(shape + (r.value_dim or r.head_dim,), dtype, device)
 
     GUARD = 512                    # elements of a known pattern before and after each pool
     PATTERN = 1.5
@@ -86,7 +89,8 @@ class KVGroup:
 
     def bytes_per_token(self, itemsize: int) -> int:
         r = self.request
-        return len(self.owners) * r.kv_heads * (r.head_dim + (r.value_dim or r.head_dim)) * itemsize
+        per_head = r.head_dim if r.values_in_keys else r.head_dim + (r.value_dim or r.head_dim)
+        return len(self.owners) * r.kv_heads * per_head * itemsize
 
     def first_needed_page(self, length: int) -> int:
         """Logical pages below this hold no key that a query at position
@@ -126,8 +130,9 @@ class SequenceCache:
                     raise CacheError(f"schedule entry {i} reads the cache of entry {src}, which owns none")
                 if kv is not None:
                     src_req = self.groups[self.entry_group[src][0]].request
-                    if (kv.kv_heads, kv.head_dim, kv.value_dim or kv.head_dim) != (
-                            src_req.kv_heads, src_req.head_dim, src_req.value_dim or src_req.head_dim):
+                    if (kv.kv_heads, kv.head_dim, kv.value_dim or kv.head_dim, kv.values_in_keys) != (
+                            src_req.kv_heads, src_req.head_dim, src_req.value_dim or src_req.head_dim,
+                            src_req.values_in_keys):
                         raise CacheError(f"schedule entry {i} cannot read entry {src}'s cache: head shapes differ")
                     # the owner gives back the pages its own window no longer reaches: a reader that looks
                     # further back would find them gone (the kernels skip pages that are not there)

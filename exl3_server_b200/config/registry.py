@@ -2,8 +2,8 @@
 
 An architecture is a configuration class (``from_dict`` / ``to_dict``) and a
 plan builder that turns a typed configuration into a ``ModelPlan``.  It is
-looked up by ``config.json``'s ``architectures[0]`` and then by its
-``model_type``.  The reference has a two-value enum and treats every
+looked up by ``config.json``'s ``architectures[0]``, then by its
+``model_type``, then by a single ``architecture`` string.  The reference has a two-value enum and treats every
 ``model_type`` that is not GLM as Llama (src/model.h:18, src/model.cpp:86-96);
 here an unknown name is an error that lists what is registered.
 """
@@ -56,13 +56,14 @@ def resolve_architecture(config_obj: Dict[str, Any]) -> Architecture:
                 tried.append(a)
                 if a in _BY_NAME:
                     return _BY_NAME[a]
-    mt = config_obj.get("model_type")
-    if isinstance(mt, str):
-        tried.append(mt)
-        if mt in _BY_NAME:
-            return _BY_NAME[mt]
+    for key in ("model_type", "architecture"):
+        mt = config_obj.get(key)
+        if isinstance(mt, str):
+            tried.append(mt)
+            if mt in _BY_NAME:
+                return _BY_NAME[mt]
     if not tried:
-        raise ConfigError("config.json: neither 'architectures' nor 'model_type' names an architecture; "
+        raise ConfigError("config.json: none of 'architectures', 'model_type' and 'architecture' names an architecture; "
                           "registered: " + ", ".join(registered_names()))
     raise ConfigError("config.json: unknown architecture " + " / ".join(repr(t) for t in tried)
                       + "; registered: " + ", ".join(registered_names()))

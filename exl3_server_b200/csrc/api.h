@@ -54,6 +54,51 @@ int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, int dtype, 
                      int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
                      cudaStream_t stream);
 size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_splits);
+// The same with values narrower than keys and rows of both pools kv_row elements apart (hdv <= hd <= kv_row, all
+// multiples of 16): out is [T, nh, hdv] and the scratch is sized with hdv.  With v_pool == k_pool the values are the
+// first hdv features of the keys (one latent row per token that every head reads).
+int exl3_attn_tokens_kv(const void* q, int64_t q_row_stride, void* out, int dtype, const void* k_pool,
+                        const void* v_pool, const int* block_table, int bt_stride, const int* tok_pos,
+                        const int* tok_seq, int T, int nh, int nkv, int hd, int hdv, int kv_row, int page, int window,
+                        float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
+                        cudaStream_t stream);
+
+// Residual update with the norm on the sublayer's output: h[t,:] += y[t,:] * rsqrt(mean(y[t,:]^2) + eps) * w (skipped
+// when y is null), then x[t,:] = h[t,:] in x_dtype (skipped when x is null).  Statistics and the sum are float32.
+int exl3_norm_add(float* h, const void* y, int y_dtype, const void* w, int w_dtype, float eps, void* x, int x_dtype,
+                  int T, int H, cudaStream_t stream);
+// xIELU, element by element, with the two raw parameters pq (any float type): for z > 0, softplus(p) z^2 + z / 2;
+// else (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2.
+int exl3_xielu(const void* z, int z_dtype, const void* pq, int pq_dtype, void* out, int out_dtype, int64_t n,
+               cudaStream_t stream);
+
+// minGRU over the packed tokens of a step.  zug [T, 3 * width]: the gate, candidate and output-gate projections
+// (biases added).  Per batch row b (tokens row_start[b] .. row_start[b + 1]) and channel, from state[slot_ids[b]]:
+// S = (1 - z) S + z c with z = sigmoid(zug[., 0:width]), c = u + 1/2 for u >= 0 else sigmoid(u), u = zug[., width:2 width];
+// y = S * silu(zug[., 2 width:]).  The last S goes back to the state.  All in float32.
+int exl3_mingru_scan(const void* zug, int zug_dtype, void* y, int y_dtype, float* state, const int* slot_ids,
+                     const int* row_start, int B, int T, int width, int max_new, cudaStream_t stream);
+
+// Latent attention, step 1, per token, from the joint projection a [T, lda] (float32 or bfloat16):
+//   cq [T, q_rank]      = rmsnorm(a[:, q_off : q_off + q_rank]) * wq
+//   cache row of token  = [ rmsnorm(a[:, kv_off : kv_off + kv_rank]) * wkv | 0 .. | rope(a[:, kv_off + kv_rank : + rot_dim]) | 0 .. ]
+//                         (the rotated part starts at rank_pad; the row is kv_row wide; skipped when pool is null)
+//   gate [T, heads]     = sigmoid(a[:, g_off : g_off + heads])  (float32)
+// The rotation takes the first rot features of the rot_dim part in half-split pairs at the token's position.
+int exl3_latent_prep(const void* a, int a_dtype, int lda, int T, int q_off, int q_rank, const void* wq, int wq_dtype,
+                     int kv_off, int kv_rank, int rot_dim, const void* wkv, int wkv_dtype, int g_off, int heads, float eps,
+                     const float* inv_freq, const float* inv_freq_lo, int rot, const int* tok_pos, const int* tok_seq,
+                     const int* block_table, int bt_stride, int page, void* pool, int pool_dtype, int kv_row,
+                     int rank_pad, void* cq, int cq_dtype, float* gate, cudaStream_t stream);
+// Products per head: out[t, h, n] = mul[t, h] * sum_k x[t, h, k] * w[h, k, n]  (n < N, k < K; mul null: 1), with
+// x[t, h, k] at x + t * x_row + h * x_head + k and out likewise; float32 sums in the order of k.  With rot_dim > 0 the
+// rot_dim features of x that follow a head's K are rotated (first rot of them, half-split pairs, at the token's
+// position) and written behind the head's outputs at out[t, h, tail_off ..]; what lies between N and tail_off and
+// behind the tail up to out_head is set to zero.  x, w and out have one element type.
+int exl3_head_gemm(const void* x, int64_t x_row, int x_head, const void* w, void* out, int64_t out_row, int out_head,
+                   int dtype, int T, int heads, int K, int N, const float* mul, int rot_dim, int rot,
+                   const float* inv_freq, const float* inv_freq_lo, const int* tok_pos, int tail_off,
+                   cudaStream_t stream);
 
 size_t exl3_argmax_scratch_bytes(int R, int V);
 // Whole prompts on tcgen05 tensor cores with TMA loads from the paged cache (bfloat16, heads of 64 or 128, pages

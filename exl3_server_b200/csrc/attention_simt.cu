@@ -20,7 +20,10 @@
 // start of the scratch memory tells it); the scratch must be zero when it is
 // first used and is left with zero counters by every launch.
 //
-// Cache layout: pool[page][kv_head][slot][head_dim], page = block_table[row][pos / page_size].
+// Cache layout: pool[page][kv_head][slot][kv_row], page = block_table[row][pos / page_size].  A row of the key
+// pool holds hd key features (kv_row >= hd elements apart); a row of the value pool holds hdv <= hd value features
+// with the same row pitch.  Ordinary attention has hdv = hd = kv_row and two pools; an attention whose values are
+// the leading features of its keys (a latent shared by all heads) passes the key pool twice with hdv < hd.
 #include "api.h"
 #include "common.cuh"
 
@@ -67,13 +70,13 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict__ out,
                    const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
-                   const int* __restrict__ tok_seq, int nh, int nkv, int hd, int page, int window,
-                   float scale, int split_keys, int max_splits, float* __restrict__ scratch,
+                   const int* __restrict__ tok_seq, int nh, int nkv, int hd, int hdv, int kv_row, int page,
+                   int window, float scale, int split_keys, int max_splits, float* __restrict__ scratch,
                    int* __restrict__ counters, int lpk) {
   constexpr int VEC = Elem<T>::vec;
   constexpr int NA = R * VEC;
-  constexpr int U = R == 1 ? 4 : 2;                  // key groups whose loads are issued together
-  extern __shared__ float smem[];                    // [ATT_WARPS][GT][hd + 2], then [2][max_splits]
+  constexpr int U = R == 1 ? 4 : (R == 2 ? 2 : 1);  // key groups whose loads are issued together
+  extern __shared__ float smem[];                    // [ATT_WARPS][GT][hdv + 2], then [2][max_splits]
   __shared__ int is_last;
   pdl_wait();
   pdl_trigger();
@@ -94,7 +97,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
     c_hi = min(hi, (c + 1) * split_keys);
   }
   const int* bt = block_table + (int64_t)tok_seq[t] * bt_stride;
-  const int rec = hd + 2;
+  const int rec = hdv + 2;
 
   for (int h0 = 0; h0 < G; h0 += GT) {
     // this lane's slice of the queries
@@ -126,7 +129,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
       const int first_page = c_lo / page, last_page = (c_hi - 1) / page;
       for (int pi = first_page + warp; pi <= last_page; pi += ATT_WARPS) {
         const int pg = bt[pi];
-        const int64_t page_base = ((int64_t)pg * nkv + g) * page * hd;
+        const int64_t page_base = ((int64_t)pg * nkv + g) * page * kv_row;
         // U groups of keys at a time: all their loads are issued before the first is used
         for (int jj0 = grp; jj0 < page; jj0 += kpw * U) {   // same trip count for every lane
           uint4 rk[U][R], rv[U][R];
@@ -139,12 +142,11 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
 #pragma unroll
             for (int r = 0; r < R; ++r) {
               const int d = (r * lpk + li) * VEC;
+              rk[u][r] = make_uint4(0, 0, 0, 0);
+              rv[u][r] = make_uint4(0, 0, 0, 0);
               if (valid[u] && d < hd) {
-                rk[u][r] = load_raw_cg(k_pool + page_base + (int64_t)jj * hd + d);
-                rv[u][r] = load_raw_cg(v_pool + page_base + (int64_t)jj * hd + d);
-              } else {
-                rk[u][r] = make_uint4(0, 0, 0, 0);
-                rv[u][r] = make_uint4(0, 0, 0, 0);
+                rk[u][r] = load_raw_cg(k_pool + page_base + (int64_t)jj * kv_row + d);
+                if (d < hdv) rv[u][r] = load_raw_cg(v_pool + page_base + (int64_t)jj * kv_row + d);
               }
             }
           }
@@ -209,23 +211,23 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           const int d = (r * lpk + li) * VEC;
-          if (d < hd) {
+          if (d < hdv) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) recp[d + e] = acc[hh][r * VEC + e];
           }
         }
-        if (li == 0) { recp[hd] = m[hh]; recp[hd + 1] = l[hh]; }
+        if (li == 0) { recp[hdv] = m[hh]; recp[hdv + 1] = l[hh]; }
       }
     }
     __syncthreads();
     // merge the warps in order 0, 1, 2, 3; thread per (head, feature)
-    for (int idx = threadIdx.x; idx < GT * hd; idx += blockDim.x) {
-      const int hh = idx / hd, d = idx - hh * hd;
+    for (int idx = threadIdx.x; idx < GT * hdv; idx += blockDim.x) {
+      const int hh = idx / hdv, d = idx - hh * hdv;
       if (h0 + hh >= G) continue;
       float mm = -INFINITY, ll = 0.0f, aa = 0.0f;
       for (int w = 0; w < ATT_WARPS; ++w) {
         const float* recp = smem + (w * GT + hh) * rec;
-        const float mo = recp[hd], lo2 = recp[hd + 1];
+        const float mo = recp[hdv], lo2 = recp[hdv + 1];
         const float mn = fmaxf(mm, mo);
         if (mn == -INFINITY) continue;
         const float cs = SoftmaxExp<T>::exp(mm - mn), co = SoftmaxExp<T>::exp(mo - mn);
@@ -235,11 +237,11 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
       }
       const int head = g * G + h0 + hh;
       if (max_splits <= 1) {
-        Elem<T>::store(out + ((int64_t)t * nh + head) * hd + d, aa / ll);
+        Elem<T>::store(out + ((int64_t)t * nh + head) * hdv + d, aa / ll);
       } else {
         float* sc = scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
         sc[d] = aa;
-        if (d == 0) { sc[hd] = mm; sc[hd + 1] = ll; }
+        if (d == 0) { sc[hdv] = mm; sc[hdv + 1] = ll; }
       }
     }
   }
@@ -260,8 +262,8 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
     const float* base = scratch + ((int64_t)t * nh + head) * max_splits * rec;
     __syncthreads();
     for (int s2 = threadIdx.x; s2 < max_splits; s2 += blockDim.x) {
-      sw[s2] = __ldcg(base + (int64_t)s2 * rec + hd);
-      sl[s2] = __ldcg(base + (int64_t)s2 * rec + hd + 1);
+      sw[s2] = __ldcg(base + (int64_t)s2 * rec + hdv);
+      sl[s2] = __ldcg(base + (int64_t)s2 * rec + hdv + 1);
     }
     __syncthreads();
     float mx = -INFINITY;
@@ -271,11 +273,11 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
     __syncthreads();
     float ll = 0.0f;
     for (int s2 = 0; s2 < max_splits; ++s2) ll += sl[s2] * sw[s2];
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    for (int d = threadIdx.x; d < hdv; d += blockDim.x) {
       float aa = 0.0f;
 #pragma unroll 4
       for (int s2 = 0; s2 < max_splits; ++s2) aa += __ldcg(base + (int64_t)s2 * rec + d) * sw[s2];
-      Elem<T>::store(out + ((int64_t)t * nh + head) * hd + d, aa / ll);
+      Elem<T>::store(out + ((int64_t)t * nh + head) * hdv + d, aa / ll);
     }
   }
   if (threadIdx.x == 0) counters[(int64_t)t * nkv + g] = 0;
@@ -317,10 +319,18 @@ __global__ void attn_combine_kernel(const float* __restrict__ scratch, T* __rest
 template <typename T, int GT, int R>
 static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const void* k_pool,
                          const void* v_pool, const int* block_table, int bt_stride, const int* tok_pos,
-                         const int* tok_seq, int T_, int nh, int nkv, int hd, int page, int window,
-                         float scale, int split_keys, int max_splits, float* scratch, int lpk,
+                         const int* tok_seq, int T_, int nh, int nkv, int hd, int hdv, int kv_row, int page,
+                         int window, float scale, int split_keys, int max_splits, float* scratch, int lpk,
                          cudaStream_t stream) {
-  const size_t smem = ((size_t)ATT_WARPS * GT * (hd + 2) + 2 * (size_t)max_splits) * sizeof(float);
+  const size_t smem = ((size_t)ATT_WARPS * GT * (hdv + 2) + 2 * (size_t)max_splits) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attn_tokens_kernel<T, GT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) {
+      set_error("attn_tokens: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+      return (int)e;
+    }
+  }
   // The first ATT_COUNTER_BYTES of scratch are counters (zero between launches); records follow.
   // worth it only for a few tokens: with many, the merge kernel overlaps better than one block's loop
   const bool fused_merge = max_splits > 1 && T_ <= 2 && (int64_t)T_ * nkv <= ATT_COUNTER_SLOTS;
@@ -329,13 +339,13 @@ static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const v
   dim3 grid(T_, nkv, max_splits);
   launch_pdl(attn_tokens_kernel<T, GT, R>, grid, dim3(ATT_WARPS * 32), smem, stream,
              static_cast<const T*>(q), q_row_stride, static_cast<T*>(out), static_cast<const T*>(k_pool),
-             static_cast<const T*>(v_pool), block_table, bt_stride, tok_pos, tok_seq, nh, nkv, hd, page, window,
-             scale, split_keys, max_splits, scratch, counters, lpk);
+             static_cast<const T*>(v_pool), block_table, bt_stride, tok_pos, tok_seq, nh, nkv, hd, hdv, kv_row, page,
+             window, scale, split_keys, max_splits, scratch, counters, lpk);
   int rc = launch_status("attn_tokens");
   if (rc) return rc;
   if (max_splits > 1 && !fused_merge) {
     launch_pdl(attn_combine_kernel<T>, dim3(T_, nh), dim3(64), (size_t)2 * max_splits * sizeof(float), stream,
-               (const float*)scratch, static_cast<T*>(out), nh, hd, max_splits);
+               (const float*)scratch, static_cast<T*>(out), nh, hdv, max_splits);
     rc = launch_status("attn_combine");
   }
   return rc;
@@ -344,7 +354,7 @@ static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const v
 template <typename T>
 static int dispatch(const void* q, int64_t q_row_stride, void* out, const void* k_pool, const void* v_pool,
                     const int* block_table, int bt_stride, const int* tok_pos, const int* tok_seq, int T_,
-                    int nh, int nkv, int hd, int page, int window, float scale, int split_keys,
+                    int nh, int nkv, int hd, int hdv, int kv_row, int page, int window, float scale, int split_keys,
                     int max_splits, float* scratch, cudaStream_t stream) {
   constexpr int VEC = Elem<T>::vec;
   const int vecs = hd / VEC;                          // 16-byte pieces per head row
@@ -354,8 +364,8 @@ static int dispatch(const void* q, int64_t q_row_stride, void* out, const void* 
   const int G = nh / nkv;
 #define EXL3_ATT(GT, RR)                                                                                 \
   return launch_tokens<T, GT, RR>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos, \
-                                  tok_seq, T_, nh, nkv, hd, page, window, scale, split_keys, max_splits, \
-                                  scratch, lpk, stream)
+                                  tok_seq, T_, nh, nkv, hd, hdv, kv_row, page, window, scale, split_keys, \
+                                  max_splits, scratch, lpk, stream)
   if (R == 1) {
     if (G == 1) EXL3_ATT(1, 1);
     if (G == 2) EXL3_ATT(2, 1);
@@ -365,6 +375,15 @@ static int dispatch(const void* q, int64_t q_row_stride, void* out, const void* 
     if (G == 1) EXL3_ATT(1, 2);
     if (G == 2) EXL3_ATT(2, 2);
     EXL3_ATT(4, 2);
+  }
+  // wide rows (latent keys): two heads a pass at most, so that a lane's queries and sums stay in registers
+  if (R == 3) {
+    if (G == 1) EXL3_ATT(1, 3);
+    EXL3_ATT(2, 3);
+  }
+  if (R <= 5) {
+    if (G == 1 || VEC == 8) EXL3_ATT(1, 5);
+    EXL3_ATT(2, 5);
   }
 #undef EXL3_ATT
   set_error("attn_tokens: head_dim %d is too large for this kernel", hd);
@@ -380,16 +399,18 @@ extern "C" size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_
   return (size_t)ATT_COUNTER_SLOTS * sizeof(int) + (size_t)T * nh * max_splits * (hd + 2) * sizeof(float);
 }
 
-extern "C" int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, int dtype,
-                                const void* k_pool, const void* v_pool, const int* block_table,
-                                int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
-                                int hd, int page, int window, float scale, int split_keys, int max_splits,
-                                float* scratch, size_t scratch_bytes, cudaStream_t stream) {
+extern "C" int exl3_attn_tokens_kv(const void* q, int64_t q_row_stride, void* out, int dtype,
+                                   const void* k_pool, const void* v_pool, const int* block_table,
+                                   int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
+                                   int hd, int hdv, int kv_row, int page, int window, float scale, int split_keys,
+                                   int max_splits, float* scratch, size_t scratch_bytes, cudaStream_t stream) {
   if (T == 0) return 0;
-  if (T < 0 || nh < 1 || nkv < 1 || nh % nkv != 0 || hd < 16 || hd % 16 != 0 || page < 1 || window < 0 ||
-      max_splits < 1 || split_keys < 0 || (max_splits > 1 && split_keys == 0)) {
-    set_error("attn_tokens: bad sizes T=%d heads=%d kv_heads=%d head_dim=%d (a multiple of 16) page=%d "
-              "window=%d split_keys=%d max_splits=%d", T, nh, nkv, hd, page, window, split_keys, max_splits);
+  if (T < 0 || nh < 1 || nkv < 1 || nh % nkv != 0 || hd < 16 || hd % 16 != 0 || hdv < 16 || hdv % 16 != 0 ||
+      hdv > hd || kv_row < hd || kv_row % 16 != 0 || page < 1 || window < 0 || max_splits < 1 || split_keys < 0 ||
+      (max_splits > 1 && split_keys == 0)) {
+    set_error("attn_tokens: bad sizes T=%d heads=%d kv_heads=%d head_dim=%d value_dim=%d row=%d (multiples of 16, "
+              "value_dim <= head_dim <= row) page=%d window=%d split_keys=%d max_splits=%d", T, nh, nkv, hd, hdv,
+              kv_row, page, window, split_keys, max_splits);
     return ERR_BAD_ARGUMENT;
   }
   if (split_keys % page != 0) {
@@ -402,18 +423,28 @@ extern "C" int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, 
     set_error("attn_tokens: q, k and v must be 16-byte aligned with a row stride in 16-byte units");
     return ERR_ALIGNMENT;
   }
-  if (exl3_attn_tokens_scratch_bytes(T, nh, hd, max_splits) > scratch_bytes) {
+  if (exl3_attn_tokens_scratch_bytes(T, nh, hdv, max_splits) > scratch_bytes) {
     set_error("attn_tokens: scratch of %zu bytes is too small, need %zu", scratch_bytes,
-              exl3_attn_tokens_scratch_bytes(T, nh, hd, max_splits));
+              exl3_attn_tokens_scratch_bytes(T, nh, hdv, max_splits));
     return ERR_SCRATCH;
   }
   if (dtype == DT_F32)
     return dispatch<float>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq, T,
-                           nh, nkv, hd, page, window, scale, split_keys, max_splits, scratch, stream);
+                           nh, nkv, hd, hdv, kv_row, page, window, scale, split_keys, max_splits, scratch, stream);
   if (dtype == DT_BF16)
     return dispatch<__nv_bfloat16>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos,
-                                   tok_seq, T, nh, nkv, hd, page, window, scale, split_keys, max_splits,
-                                   scratch, stream);
+                                   tok_seq, T, nh, nkv, hd, hdv, kv_row, page, window, scale, split_keys,
+                                   max_splits, scratch, stream);
   set_error("attn_tokens: unsupported element type %d", dtype);
   return ERR_UNSUPPORTED;
+}
+
+extern "C" int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, int dtype,
+                                const void* k_pool, const void* v_pool, const int* block_table,
+                                int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
+                                int hd, int page, int window, float scale, int split_keys, int max_splits,
+                                float* scratch, size_t scratch_bytes, cudaStream_t stream) {
+  return exl3_attn_tokens_kv(q, q_row_stride, out, dtype, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq, T,
+                             nh, nkv, hd, hd, hd, page, window, scale, split_keys, max_splits, scratch, scratch_bytes,
+                             stream);
 }

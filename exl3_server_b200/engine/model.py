@@ -26,11 +26,12 @@ def plan_manifest(plan: ModelPlan) -> List[TensorSpec]:
     specs: List[TensorSpec] = list(embedding_class(plan.embedding.kind).tensor_specs(plan.embedding))
     for layer in plan.layers:
         specs += mixer_class(layer.mixer.kind).tensor_specs(layer.mixer, layer.names["mixer"])
-        specs += feed_forward_class(layer.feed_forward.kind).tensor_specs(layer.feed_forward,
-                                                                         layer.names["feed_forward"])
         specs += norm_class(layer.mixer_norm.kind).tensor_specs(layer.mixer_norm, layer.names["mixer_norm"])
-        specs += norm_class(layer.feed_forward_norm.kind).tensor_specs(layer.feed_forward_norm,
-                                                                      layer.names["feed_forward_norm"])
+        if layer.feed_forward is not None:
+            specs += feed_forward_class(layer.feed_forward.kind).tensor_specs(layer.feed_forward,
+                                                                             layer.names["feed_forward"])
+            specs += norm_class(layer.feed_forward_norm.kind).tensor_specs(layer.feed_forward_norm,
+                                                                          layer.names["feed_forward_norm"])
     specs += norm_class(plan.final_norm.kind).tensor_specs(plan.final_norm, plan.final_norm_name)
     specs += head_class(plan.head.kind).tensor_specs(plan.head)
     return specs
@@ -47,11 +48,13 @@ class Model:
         self.blocks = []
         for layer in plan.layers:
             mixer = mixer_class(layer.mixer.kind)(layer.mixer, tensors, layer.names["mixer"], ctx)
-            ff = feed_forward_class(layer.feed_forward.kind)(layer.feed_forward, tensors,
-                                                             layer.names["feed_forward"], ctx)
             n1 = norm_class(layer.mixer_norm.kind)(layer.mixer_norm, tensors, layer.names["mixer_norm"], ctx)
-            n2 = norm_class(layer.feed_forward_norm.kind)(layer.feed_forward_norm, tensors,
-                                                          layer.names["feed_forward_norm"], ctx)
+            ff = n2 = None
+            if layer.feed_forward is not None:
+                ff = feed_forward_class(layer.feed_forward.kind)(layer.feed_forward, tensors,
+                                                                 layer.names["feed_forward"], ctx)
+                n2 = norm_class(layer.feed_forward_norm.kind)(layer.feed_forward_norm, tensors,
+                                                              layer.names["feed_forward_norm"], ctx)
             self.blocks.append(arrangement_class(layer.arrangement)(layer, mixer, ff, n1, n2))
         self.final_norm = norm_class(plan.final_norm.kind)(plan.final_norm, tensors, plan.final_norm_name, ctx)
         self.head = head_class(plan.head.kind)(plan.head, tensors, self.embedding, ctx)

@@ -476,6 +476,118 @@ def attn_tokens(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
     return out
 
 
+def attn_tokens_kv(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor,
+                   v_pool: torch.Tensor, block_table: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
+                   T: int, heads: int, kv_heads: int, head_dim: int, value_dim: int, kv_row: int, page: int,
+                   window: int, scale: float, split_keys: int, max_splits: int,
+                   scratch: Optional[torch.Tensor]) -> torch.Tensor:
+    """``attn_tokens`` with values of ``value_dim <= head_dim`` features and rows of both pools ``kv_row`` elements
+    apart; ``out`` is ``[T, heads, value_dim]`` and the scratch is sized with ``value_dim``.  With ``v_pool`` the
+    key pool itself, the values are the keys' first ``value_dim`` features."""
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelLibraryError("attn_tokens_kv: q, cache and out differ in element type")
+    nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
+    _check(library().exl3_attn_tokens_kv(
+        _ptr(q), _c_int64(q_row_stride), _ptr(out), _c_int(dtype_code(q.dtype)), _ptr(k_pool), _ptr(v_pool),
+        _ptr(block_table), _c_int(block_table.stride(0)), _ptr(tok_pos), _ptr(tok_seq), _c_int(T),
+        _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(value_dim), _c_int(kv_row), _c_int(page),
+        _c_int(window), _c_float(scale), _c_int(split_keys), _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes),
+        _stream()), "attn_tokens_kv")
+    return out
+
+
+def norm_add(h: torch.Tensor, y: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+             x_dtype: Optional[torch.dtype]) -> Optional[torch.Tensor]:
+    """``h += y * rsqrt(mean(y^2) + eps) * weight`` per row, in place and in float32 (nothing when ``y`` is None);
+    returns ``h`` in ``x_dtype`` as a new tensor (None when ``x_dtype`` is None)."""
+    T, H = h.shape
+    if h.dtype != torch.float32:
+        raise KernelLibraryError("norm_add: the residual stream must be float32")
+    _contig(h, "h")
+    if y is not None:
+        _contig(y, "y")
+        if tuple(y.shape) != (T, H) or weight is None or weight.numel() != H:
+            raise KernelLibraryError(f"norm_add: y {tuple(y.shape)} / weight do not fit h {tuple(h.shape)}")
+    x = torch.empty((T, H), dtype=x_dtype, device=h.device) if x_dtype is not None else None
+    if y is None and x is None:
+        return None
+    _check(library().exl3_norm_add(
+        _ptr(h), _ptr(y), _c_int(dtype_code(y.dtype) if y is not None else 0), _ptr(weight),
+        _c_int(dtype_code(weight.dtype) if weight is not None else 0), _c_float(eps), _ptr(x),
+        _c_int(dtype_code(x.dtype) if x is not None else 0), _c_int(T), _c_int(H), _stream()), "norm_add")
+    return x
+
+
+def xielu(z: torch.Tensor, pq: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """xIELU of every element with the raw parameter pair ``pq`` (see outnorm.cu)."""
+    _contig(z, "z")
+    if pq.numel() != 2:
+        raise KernelLibraryError("xielu: the activation takes two parameters")
+    out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+    _check(library().exl3_xielu(_ptr(z), _c_int(dtype_code(z.dtype)), _ptr(pq), _c_int(dtype_code(pq.dtype)),
+                                _ptr(out), _c_int(dtype_code(out.dtype)), _c_int64(z.numel()), _stream()), "xielu")
+    return out
+
+
+def mingru_scan(zug: torch.Tensor, state: torch.Tensor, slot_ids: torch.Tensor, row_start: torch.Tensor,
+                rows: int, width: int, max_new: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """The minGRU recurrence over a step's packed tokens (see recurrent.cu): ``zug [T, 3 * width]``, ``state
+    [slots, width]`` float32 read and written at ``slot_ids``; returns ``S_t * silu(g_t)`` as ``[T, width]``."""
+    T = zug.shape[0]
+    _contig(zug, "zug")
+    _contig(state, "state")
+    if zug.shape[1] != 3 * width or state.dtype != torch.float32 or state.shape[1] != width:
+        raise KernelLibraryError(f"mingru_scan: zug {tuple(zug.shape)} / state {tuple(state.shape)} do not fit width {width}")
+    if slot_ids.dtype != torch.int32 or row_start.dtype != torch.int32:
+        raise KernelLibraryError("mingru_scan: slot_ids and row_start must be int32")
+    y = torch.empty((T, width), dtype=out_dtype, device=zug.device)
+    _check(library().exl3_mingru_scan(_ptr(zug), _c_int(dtype_code(zug.dtype)), _ptr(y), _c_int(dtype_code(y.dtype)),
+                                      _ptr(state), _ptr(slot_ids), _ptr(row_start), _c_int(rows), _c_int(T),
+                                      _c_int(width), _c_int(max_new), _stream()), "mingru_scan")
+    return y
+
+
+def latent_prep(a: torch.Tensor, q_off: int, q_rank: int, wq: torch.Tensor, kv_off: int, kv_rank: int, rot_dim: int,
+                wkv: Optional[torch.Tensor], g_off: int, heads: int, eps: float, inv_freq: Optional[torch.Tensor],
+                rot: int, tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor, page: int,
+                pool: Optional[torch.Tensor], kv_row: int, rank_pad: int, cq_dtype: torch.dtype):
+    """Latent attention's step between the joint input projection ``a`` and the rest (see latent.cu): returns the
+    normed query latent ``[T, q_rank]`` and the float32 gates ``[T, heads]``; writes each token's row of the cache
+    (``pool``; None for a layer that reads another layer's rows)."""
+    T = a.shape[0]
+    _contig(a, "a")
+    f_hi, f_lo = (_rotary_rows(inv_freq, rot, "latent_prep") if rot > 0 and inv_freq is not None
+                  else (_c_void_p(0), _c_void_p(0)))
+    cq = torch.empty((T, q_rank), dtype=cq_dtype, device=a.device)
+    gate = torch.empty((T, heads), dtype=torch.float32, device=a.device)
+    _check(library().exl3_latent_prep(
+        _ptr(a), _c_int(dtype_code(a.dtype)), _c_int(a.shape[1]), _c_int(T), _c_int(q_off), _c_int(q_rank), _ptr(wq),
+        _c_int(dtype_code(wq.dtype)), _c_int(kv_off), _c_int(kv_rank), _c_int(rot_dim), _ptr(wkv),
+        _c_int(dtype_code(wkv.dtype) if wkv is not None else 0), _c_int(g_off), _c_int(heads), _c_float(eps), f_hi, f_lo,
+        _c_int(rot), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), _c_int(block_table.stride(0)), _c_int(page),
+        _ptr(pool), _c_int(dtype_code(pool.dtype) if pool is not None else 0), _c_int(kv_row), _c_int(rank_pad),
+        _ptr(cq), _c_int(dtype_code(cq.dtype)), _ptr(gate), _stream()), "latent_prep")
+    return cq, gate
+
+
+def head_gemm(x: torch.Tensor, x_row: int, x_head: int, w: torch.Tensor, out: torch.Tensor, out_row: int,
+              out_head: int, T: int, heads: int, K: int, N: int, mul: Optional[torch.Tensor] = None, rot_dim: int = 0,
+              rot: int = 0, inv_freq: Optional[torch.Tensor] = None, tok_pos: Optional[torch.Tensor] = None,
+              tail_off: int = 0) -> torch.Tensor:
+    """``out[t, h, n] = mul[t, h] * sum_k x[t, h, k] w[h, k, n]`` with the given row and head pitches (elements);
+    with ``rot_dim`` the features behind a head's ``K`` are rotated and written at ``tail_off`` (see latent.cu)."""
+    if w.dtype != x.dtype or out.dtype != x.dtype or tuple(w.shape) != (heads, K, N):
+        raise KernelLibraryError(f"head_gemm: w {tuple(w.shape)} must be {(heads, K, N)} in the type of x and out")
+    _contig(w, "w")
+    f_hi, f_lo = (_rotary_rows(inv_freq, rot, "head_gemm") if rot > 0 and inv_freq is not None
+                  else (_c_void_p(0), _c_void_p(0)))
+    _check(library().exl3_head_gemm(
+        _ptr(x), _c_int64(x_row), _c_int(x_head), _ptr(w), _ptr(out), _c_int64(out_row), _c_int(out_head),
+        _c_int(dtype_code(x.dtype)), _c_int(T), _c_int(heads), _c_int(K), _c_int(N), _ptr(mul), _c_int(rot_dim),
+        _c_int(rot), f_hi, f_lo, _ptr(tok_pos), _c_int(tail_off), _stream()), "head_gemm")
+    return out
+
+
 def attn_prefill_tc_supported(dtype: torch.dtype, head_dim: int, page: int) -> bool:
     return bool(library().exl3_attn_prefill_tc_supported(_c_int(dtype_code(dtype)), _c_int(head_dim), _c_int(page)))
 

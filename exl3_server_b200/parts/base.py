@@ -40,11 +40,13 @@ class BuildContext:
 class KVRequest:
     """Keys and values for every position (window 0) or the last ``window``.  ``value_dim`` is the width of a
     value per head when it differs from the key's (0: the same), as in mixers that keep narrow keys or a
-    compressed value."""
+    compressed value.  ``values_in_keys``: there is no pool of values; a mixer whose values are part of what it
+    keeps as keys (one latent row per token) gets the key pool as both."""
     kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: int = 0
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)
@@ -65,6 +67,9 @@ class ResidualStream:
         # (norm, RawNormed): what ``norm`` needs for its output over the residual as it stands, left by a
         # projection that folded its output into the residual in its own kernel (see NormAfter)
         self.normed = None
+        # the residual as it stands in the activation type, when a block has left it (arrangements whose sublayers
+        # read the residual itself); whoever changes ``h`` afterwards forgets it
+        self.act: Optional[torch.Tensor] = None
 
     def push(self, y: torch.Tensor, scale: float) -> None:
         if self.pending is not None:
@@ -72,6 +77,7 @@ class ResidualStream:
         self.pending = y
         self.pending_scale = scale
         self.normed = None
+        self.act = None
 
     def take_normed(self, norm):
         """What a projection has left for ``norm`` over the residual as it stands (a ``RawNormed``), or None."""

@@ -4,6 +4,11 @@
 (src/model.cpp:556-586, with rho = 1 there).  The sublayer output is
 multiplied by ``residual_scale`` and then added, in float32, inside the next
 norm's kernel.
+
+``outnorm``: the sublayers read the residual itself and the norm sits on their
+output: ``h += norm1(mixer(h))`` then ``h += norm2(ff(h))``.  The norm, the add
+(float32) and the cast of the new residual for the next sublayer are one kernel.
+A layer of this kind may have no feed-forward at all.
 """
 from __future__ import annotations
 
@@ -52,4 +57,26 @@ class PreNormBlock:
                                               self.feed_forward_norm) if hasattr(p, "weight_bytes"))
 
 
+class OutNormBlock:
+    def __init__(self, spec: LayerSpec, mixer, feed_forward, mixer_norm, feed_forward_norm):
+        if spec.residual_scale != 1.0:
+            raise ValueError("outnorm: a scale on the sublayer's output would be undone by the norm")
+        self.spec = spec
+        self.mixer = mixer
+        self.feed_forward = feed_forward              # None: the layer is its mixer only
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+
+    def forward(self, stream: ResidualStream, batch, kv, state) -> None:
+        x = stream.act if stream.act is not None and stream.pending is None else self.mixer_norm.add_normed(stream, None)
+        x = self.mixer_norm.add_normed(stream, self.mixer.forward(x, batch, kv, state))
+        if self.feed_forward is not None:
+            self.feed_forward_norm.add_normed(stream, self.feed_forward.forward(x, batch))
+
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in (self.mixer, self.feed_forward, self.mixer_norm, self.feed_forward_norm)
+                   if p is not None and hasattr(p, "weight_bytes"))
+
+
 register_arrangement("prenorm", PreNormBlock)
+register_arrangement("outnorm", OutNormBlock)

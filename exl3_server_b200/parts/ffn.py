@@ -1,7 +1,15 @@
-"""The dense gated feed-forward: ``y = (silu(r Wg^T) * (r Wu^T)) Wd^T``
+"""Feed-forwards.
+
+``swiglu``, the dense gated feed-forward: ``y = (silu(r Wg^T) * (r Wu^T)) Wd^T``
 (src/model.cpp:583-586; the reference applies SiLU unconditionally).  Gate and
 up projections are one fused matrix; the product ``silu(g) * u`` is float32
 inside its kernel.
+
+``dense``: ``y = act(r Wu^T) Wd^T`` with an activation named in the spec's
+``params["activation"]``.  ``xielu`` has two learned numbers ``p, q`` (tensor
+``act``): ``softplus(p) z^2 + z/2`` for ``z > 0`` and
+``(1/2 + softplus(q)) (exp(z) - 1 - z) + z/2`` otherwise; it is computed in
+float32 from the float32 results of the up projection.
 """
 from __future__ import annotations
 
@@ -64,4 +72,45 @@ class SwiGLU:
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
 
 
+def _xielu(z: torch.Tensor, tensors, out_dtype):
+    return K.xielu(z, tensors["act"], out_dtype)
+
+
+# name -> (parameter tensors as (suffix, shape), function(z, {suffix: tensor}, out_dtype))
+ACTIVATIONS = {"xielu": ((("act", (2,)),), _xielu)}
+
+
+class DenseFeedForward:
+    @staticmethod
+    def _activation(spec: FeedForwardSpec):
+        name = spec.params.get("activation", "xielu")
+        try:
+            return ACTIVATIONS[name]
+        except KeyError:
+            raise ValueError(f"dense feed-forward: no activation named {name!r}; known: {sorted(ACTIVATIONS)}") from None
+
+    @classmethod
+    def tensor_specs(cls, spec: FeedForwardSpec, prefix: str) -> List[TensorSpec]:
+        extra, _ = cls._activation(spec)
+        return [TensorSpec(prefix + "up", (spec.inner, spec.width)),
+                TensorSpec(prefix + "down", (spec.width, spec.inner))] + \
+               [TensorSpec(prefix + name, shape) for name, shape in extra]
+
+    def __init__(self, spec: FeedForwardSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
+        self.spec = spec
+        self.dtype = ctx.dtype
+        extra, self.act = self._activation(spec)
+        self.act_tensors = {name: tensors[prefix + name].contiguous() for name, _ in extra}
+        self.up = Linear(tensors[prefix + "up"], None, ctx.dtype)
+        self.down = Linear(tensors[prefix + "down"], None, ctx.dtype)
+
+    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+        z = self.up(x, out_dtype=torch.float32)
+        return self.down(self.act(z, self.act_tensors, self.dtype), out_dtype=torch.float32)
+
+    def weight_bytes(self) -> int:
+        return self.up.weight_bytes() + self.down.weight_bytes()
+
+
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("dense", DenseFeedForward)

@@ -4,6 +4,9 @@
 (no ``1 + w``), as the reference's ``mx::fast::rms_norm`` calls use it
 (src/model.cpp:556, 582, 589).  The sum of squares, the reciprocal root and the
 residual add ``h += scale * y`` are float32.
+
+The same norm also serves layers that norm a sublayer's output instead of its
+input (``add_normed``: ``h += rmsnorm(y) * w``; the ``outnorm`` arrangement).
 """
 from __future__ import annotations
 
@@ -21,11 +24,11 @@ from .spec import NormSpec
 class RMSNorm:
     @staticmethod
     def tensor_specs(spec: NormSpec, prefix: str) -> List[TensorSpec]:
-        return [TensorSpec(prefix + "weight", (spec.width,), init="ones")]
+        return [TensorSpec(prefix + spec.params.get("suffix", "weight"), (spec.width,), init="ones")]
 
     def __init__(self, spec: NormSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
         self.spec = spec
-        w = tensors[prefix + "weight"]
+        w = tensors[prefix + spec.params.get("suffix", "weight")]     # the tensor's name is prefix + suffix
         # a weight stored in 32-bit stays 32-bit; the kernel reads either
         self.weight = w.contiguous() if w.dtype == torch.float32 else w.to(ctx.dtype).contiguous()
         self.out_dtype = ctx.dtype
@@ -42,8 +45,22 @@ class RMSNorm:
                 return left
             return left.materialize(out_scale, rows)
         y, s = stream.take()
+        if y is not None:
+            stream.act = None
         return K.add_rmsnorm(stream.h, y, s, self.weight, self.spec.eps, self.out_dtype,
                              out_scale=out_scale, rows=rows)
+
+    def add_normed(self, stream: ResidualStream, y: Optional[torch.Tensor]) -> torch.Tensor:
+        """The norm on a sublayer's OUTPUT: ``h += y * rsqrt(mean(y^2) + eps) * w`` in float32; returns the new
+        residual in the activation type, which the next sublayer reads (``h`` itself in the float32 path).  With
+        ``y`` None nothing is added and the residual is only handed over."""
+        if stream.pending is not None:
+            raise RuntimeError("the residual stream holds an output that was not folded in")
+        stream.normed = None
+        x_dtype = None if self.out_dtype == torch.float32 else self.out_dtype
+        x = K.norm_add(stream.h, y, self.weight if y is not None else None, self.spec.eps, x_dtype)
+        stream.act = x if x is not None else stream.h
+        return stream.act
 
     def fuse_args(self):
         """``(weight, eps, width)`` for a projection kernel that prepares this norm (see ``NormAfter``)."""

@@ -61,9 +61,9 @@ class LayerSpec:
     """One layer: which parts, in which arrangement, under which tensor names."""
     arrangement: str              # registered block arrangement, e.g. "prenorm"
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]    # None: a layer of the mixer only (arrangements that allow it)
     mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward_norm: Optional[NormSpec]
     residual_scale: float         # sublayer outputs are multiplied by this before the add
     # tensor-name prefixes in the checkpoint, by role
     names: Dict[str, str] = field(default_factory=dict, hash=False, compare=False)
