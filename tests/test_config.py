@@ -97,7 +97,7 @@ def test_registry_names_and_unknown():
     assert resolve_architecture({"model_type": "llama"}).build_plan is build_plan
     with pytest.raises(ConfigError, match="registered: .*llama"):
         resolve_architecture({"architectures": ["GptOssForCausalLM"], "model_type": "gpt_oss"})
-    with pytest.raises(ConfigError, match="neither"):
+    with pytest.raises(ConfigError, match="names an architecture"):
         resolve_architecture({})
 
 
