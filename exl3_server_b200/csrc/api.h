@@ -63,6 +63,19 @@ int exl3_attn_tokens_kv(const void* q, int64_t q_row_stride, void* out, int dtyp
                         float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
                         cudaStream_t stream);
 
+// Attention over latent rows on the tensor cores (bfloat16; see attention_latent.cu).  q [T * H, dk] and out
+// [T * H, dv] hold the rows of each sequence's tokens of this step head by head; the pool holds one row of dk
+// features per key, page = 64 keys, whose first dv features are the values.  Batch row b has the tokens
+// row_start[b] .. row_start[b + 1], the first of them at position row_pos0[b]; max_new is the most tokens of any row.
+// n_splits > 1: chunks of pages_per_chunk pages, merged through scratch (exl3_attn_latent_scratch_bytes).
+// exl3_attn_latent_row_tile: sixteens of rows a block takes for these sizes (0: dk does not fit shared memory).
+int exl3_attn_latent_row_tile(int dk, int max_rows);
+size_t exl3_attn_latent_scratch_bytes(int T, int H, int dv, int n_splits);
+int exl3_attn_latent(const void* q, void* out, const void* pool, const int* block_table, int bt_stride,
+                     const int* row_start, const int* row_pos0, int B, int T, int max_new, int H, int dk, int dv, int page,
+                     float scale, int pages_per_chunk, int n_splits, float* scratch, size_t scratch_bytes,
+                     cudaStream_t stream);
+
 // Residual update with the norm on the sublayer's output: h[t,:] += y[t,:] * rsqrt(mean(y[t,:]^2) + eps) * w (skipped
 // when y is null), then x[t,:] = h[t,:] in x_dtype (skipped when x is null).  Statistics and the sum are float32.
 int exl3_norm_add(float* h, const void* y, int y_dtype, const void* w, int w_dtype, float eps, void* x, int x_dtype,

@@ -496,6 +496,42 @@ def attn_tokens_kv(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool
     return out
 
 
+def attn_latent_supported(dtype: torch.dtype, dk: int, dv: int, page: int) -> bool:
+    """Whether the tensor-core kernel for latent rows takes these sizes."""
+    return (dtype == torch.bfloat16 and page == 64 and dk % 16 == 0 and dv % 16 == 0 and dv <= min(dk, 512)
+            and int(library().exl3_attn_latent_row_tile(_c_int(dk), _c_int(16))) >= 1)
+
+
+def attn_latent_row_tile(dk: int, max_rows: int) -> int:
+    """Rows of one sequence that a block of the kernel takes for these sizes."""
+    return 16 * int(library().exl3_attn_latent_row_tile(_c_int(dk), _c_int(max_rows)))
+
+
+def attn_latent_scratch_bytes(T: int, heads: int, dv: int, n_splits: int) -> int:
+    lib = library()
+    lib.exl3_attn_latent_scratch_bytes.restype = _c_size_t
+    return int(lib.exl3_attn_latent_scratch_bytes(_c_int(T), _c_int(heads), _c_int(dv), _c_int(n_splits)))
+
+
+def attn_latent(q: torch.Tensor, out: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
+                row_start: torch.Tensor, row_pos0: torch.Tensor, rows: int, T: int, max_new: int, heads: int, dk: int,
+                dv: int, page: int, scale: float, pages_per_chunk: int, n_splits: int,
+                scratch: Optional[torch.Tensor]) -> torch.Tensor:
+    """Attention of a step's tokens over latent rows on the tensor cores (see attention_latent.cu): ``q [T, heads *
+    dk]``, ``out [T, heads * dv]``, one cached row of ``dk`` features per key whose first ``dv`` are the values."""
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16:
+        raise KernelLibraryError("attn_latent: q, out and the cache must be bfloat16")
+    _contig(q, "q")
+    _contig(out, "out")
+    nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
+    _check(library().exl3_attn_latent(
+        _ptr(q), _ptr(out), _ptr(pool), _ptr(block_table), _c_int(block_table.stride(0)), _ptr(row_start),
+        _ptr(row_pos0), _c_int(rows), _c_int(T), _c_int(max_new), _c_int(heads), _c_int(dk), _c_int(dv), _c_int(page),
+        _c_float(scale), _c_int(pages_per_chunk), _c_int(n_splits), _ptr(scratch), _c_size_t(nbytes), _stream()),
+        "attn_latent")
+    return out
+
+
 def norm_add(h: torch.Tensor, y: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
              x_dtype: Optional[torch.dtype]) -> Optional[torch.Tensor]:
     """``h += y * rsqrt(mean(y^2) + eps) * weight`` per row, in place and in float32 (nothing when ``y`` is None);

@@ -9,7 +9,7 @@ inside its kernel.
 ``params["activation"]``.  ``xielu`` has two learned numbers ``p, q`` (tensor
 ``act``): ``softplus(p) z^2 + z/2`` for ``z > 0`` and
 ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z/2`` otherwise; it is computed in
-float32 from the float32 results of the up projection.
+float32 (from float32 results of the up projection where the projection's kernel has them).
 """
 from __future__ import annotations
 
@@ -105,8 +105,8 @@ class DenseFeedForward:
         self.down = Linear(tensors[prefix + "down"], None, ctx.dtype)
 
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
-        z = self.up(x, out_dtype=torch.float32)
-        return self.down(self.act(z, self.act_tensors, self.dtype), out_dtype=torch.float32)
+        z = self.up(x, out_dtype=self.up.wide_dtype(x.shape[0]))
+        return self.down(self.act(z, self.act_tensors, self.dtype), out_dtype=self.down.wide_dtype(x.shape[0]))
 
     def weight_bytes(self) -> int:
         return self.up.weight_bytes() + self.down.weight_bytes()

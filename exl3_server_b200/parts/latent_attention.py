@@ -122,7 +122,7 @@ class LatentAttention:
         if kv.owns != self.owner:
             raise RuntimeError("latent attention: the plan's cache_from and the layer's own rows disagree")
         T, H, dt = x.shape[0], self.H, self.ctx.dtype
-        a = self.inp(x, out_dtype=torch.float32)
+        a = self.inp(x, out_dtype=self.inp.wide_dtype(T))
         cq, gate = K.latent_prep(a, self.q_off, self.q_rank, self.w_dq_norm, self.kv_off, self.kv_rank, self.rot_dim,
                                  self.w_dkv_norm, self.g_off, H, self.eps, self.inv_freq, self.rot, batch.tok_pos,
                                  batch.tok_seq, kv.block_table, kv.page_size, kv.k if self.owner else None, self.row,
@@ -138,11 +138,20 @@ class LatentAttention:
         o = torch.empty((T, H * self.vdim), dtype=dt, device=x.device)
         K.head_gemm(ol, H * self.rank_pad, self.rank_pad, self.w_uv, o, H * self.vdim, self.vdim, T, H, self.kv_rank,
                     self.vdim, mul=gate)
-        return self.o(o, out_dtype=torch.float32)
+        return self.o(o, out_dtype=self.o.wide_dtype(T))
 
     def attend(self, ql: torch.Tensor, ol: torch.Tensor, batch, kv) -> None:
         """Attention of the step's tokens over the cached rows: ``H`` query heads on one row per key."""
         T = ql.shape[0]
+        if K.attn_latent_supported(ql.dtype, self.row, self.rank_pad, kv.page_size):
+            # bfloat16: both products on the tensor cores, a block per tile of a sequence's (token, head) rows
+            per, n = self._chunks(batch, kv.page_size, ql.device)
+            scratch = None
+            if n > 1:
+                scratch = batch.workspace.floats(K.attn_latent_scratch_bytes(T, self.H, self.rank_pad, n) // 4)
+            K.attn_latent(ql, ol, kv.k, kv.block_table, batch.row_start, batch.row_pos0, batch.n_rows, T, batch.max_new,
+                          self.H, self.row, self.rank_pad, kv.page_size, self.scale, per, n, scratch)
+            return
         split = max(SPLIT_KEYS, kv.page_size)
         if split % kv.page_size:
             split = kv.page_size * (split // kv.page_size + 1)
@@ -152,6 +161,19 @@ class LatentAttention:
             scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, self.H, self.rank_pad, n) // 4)
         K.attn_tokens_kv(ql, ql.stride(0), ol, kv.k, kv.k, kv.block_table, batch.tok_pos, batch.tok_seq, T, self.H, 1,
                          self.row, self.rank_pad, self.row, kv.page_size, 0, self.scale, split, n, scratch)
+
+    def _chunks(self, batch, page: int, device):
+        """``(pages per chunk, chunks)`` for the tensor-core kernel: one chunk when the step's tiles of rows already
+        give every SM a block (prompts, large batches); else the keys are cut into as many chunks of whole pages as
+        it takes to get there, none shorter than four pages.  The choice depends on the step's size, not on a token's
+        position: results differ between batch sizes by rounding."""
+        pages = max(1, (batch.max_kv_len + page - 1) // page)
+        tile = K.attn_latent_row_tile(self.row, batch.max_new * self.H)
+        blocks = batch.n_rows * ((batch.max_new * self.H + tile - 1) // tile)
+        want = max(1, K.sm_count(device) // max(1, blocks))
+        n = max(1, min(want, pages // 4))
+        per = (pages + n - 1) // n
+        return per, (pages + per - 1) // per
 
     def weight_bytes(self) -> int:
         own = sum(t.numel() * t.element_size() for t in (self.w_uk, self.w_uv))

@@ -130,6 +130,15 @@ class Linear:
                                 inv_freq, rot, pos_scale, heads, kv_heads, head_dim, page,
                                 kv.k if write else None, kv.v if write else None, write)
 
+    def wide_dtype(self, rows: int) -> torch.dtype:
+        """The element type in which ``rows`` rows of results cost nothing extra to get in 32 bits: float32 from the
+        kernels that stream the weights for few rows (their sums are float32 anyway), the model's own type from the
+        kernels for many rows, which write 16-bit tiles.  For callers whose next step (a norm, a gate, a recurrence)
+        computes in float32 and takes either."""
+        if self.dtype == torch.float32 or rows <= SKINNY_ROWS:
+            return torch.float32
+        return self.dtype
+
     def streams_weights(self, rows: int) -> bool:
         """Whether ``rows`` rows of input go through a kernel that reads the weights once."""
         return self._streaming_kernel(rows) is not None

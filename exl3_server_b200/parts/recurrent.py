@@ -67,10 +67,10 @@ class MinGRU:
     def forward(self, x: torch.Tensor, batch, kv, state) -> torch.Tensor:
         if state is None:
             raise RuntimeError("mingru needs its per-sequence state")
-        zug = self.zug(x, out_dtype=torch.float32)
+        zug = self.zug(x, out_dtype=self.zug.wide_dtype(x.shape[0]))
         y = K.mingru_scan(zug, state, batch.slot_ids, batch.row_start, batch.n_rows, self.inner, batch.max_new,
                           self.ctx.dtype)
-        return self.o(y, out_dtype=torch.float32)
+        return self.o(y, out_dtype=self.o.wide_dtype(x.shape[0]))
 
     def weight_bytes(self) -> int:
         return self.zug.weight_bytes() + self.o.weight_bytes()
