@@ -25,6 +25,13 @@ fallback.
 ``--only decode|prefill|unequal`` with ``--sizes NAME`` runs one part at any of
 the size tables and prints a short JSON line (for profiling small cases).
 
+``--only designs`` measures the Rigitar decoder (latent attention, minGRU and
+dense xIELU layers) beside the Llama-family decoder at equal width, depth, head
+count and feed-forward width, with random weights: one prompt of
+``--prefill-tokens`` tokens and decode steps at ``--batch`` and ``--context``,
+for each of the size pairs in ``DESIGN_SIZES`` (or the one named by
+``--design-sizes``); ``--design-arch`` runs one of the two only (for profiling).
+
 Only one GPU is supported: for N > 1 it says so and exits with 2.
 """
 from __future__ import annotations
@@ -109,8 +116,68 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# Size pairs for ``--only designs``: width, layers, heads, feed-forward width, vocabulary; the Llama side has heads of
+# ``head_dim`` on ``kv_heads`` key/value heads; the Rigitar side has latent attention with these sizes in half of its
+# layers (every second of them reading the rows of the one before), minGRU of the model's width in the others, and
+# the dense feed-forward in all.
+DESIGN_SIZES = {
+    "w2048": dict(width=2048, layers=8, heads=16, ff=5632, vocab=32000, head_dim=128, kv_heads=16,
+                  latent=dict(dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=512)),
+    "w4096": dict(width=4096, layers=4, heads=32, ff=11008, vocab=32000, head_dim=128, kv_heads=8,
+                  latent=dict(dim=128, rot_dim=64, vdim=128, q_rank=1536, kv_rank=512)),
+}
+
+
+def design_configs(name: str):
+    """(Rigitar configuration, Llama configuration) of one size pair."""
+    import exl3_server_b200 as E
+    from exl3_server_b200.config.rigitar import RigitarConfig, RigitarLayer
+    z = DESIGN_SIZES[name]
+    lat = z["latent"]
+    layers = []
+    for i in range(z["layers"]):
+        mlp = {"kind": "dense", "ff": z["ff"]}
+        if i % 4 in (1, 2):
+            m = dict(heads=z["heads"], scale=(lat["dim"] + lat["rot_dim"]) ** -0.5,
+                     rot={"base": 10000.0, "dims": lat["rot_dim"]}, **lat)
+            if i % 4 == 2:
+                m["kv_from"] = i - 1
+            layers.append(RigitarLayer("latent_attention", m, mlp))
+        else:
+            layers.append(RigitarLayer("mingru", {"width": z["width"]}, mlp))
+    rig = RigitarConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, layers=layers)
+    llama = E.LlamaConfig(hidden_size=z["width"], num_hidden_layers=z["layers"], num_attention_heads=z["heads"],
+                          num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"], intermediate_size=z["ff"],
+                          vocab_size=z["vocab"], tie_word_embeddings=False, max_position_embeddings=0)
+    return rig, llama
+
+
 class Rig:
     """A random-weight model of one of the size tables with a cache, and the timed pieces."""
+
+    @classmethod
+    def of_config(cls, name: str, cfg, cache_tokens: int, max_slots: int) -> "Rig":
+        """The same for any registered architecture's typed configuration."""
+        import torch
+        import exl3_server_b200 as E
+        from exl3_server_b200.config.registry import resolve_architecture
+        from exl3_server_b200.engine.model import Model, plan_manifest
+        from exl3_server_b200.weights.random_init import random_tensors
+        self = cls.__new__(cls)
+        self.torch, self.E, self.name, self.cfg = torch, E, name, cfg
+        dev = torch.device("cuda:0")
+        t0 = time.time()
+        plan = resolve_architecture(cfg.to_dict()).build_plan(cfg)
+        self.layers = self.layers_full = len(plan.layers)
+        self.vocab = plan.head.vocab
+        tensors = dict(random_tensors(plan_manifest(plan), seed=0, std=0.02, norm_std=None, dtype=torch.bfloat16,
+                                      device=dev))
+        self.model = Model(plan, tensors, torch.bfloat16, dev)
+        del tensors
+        self.engine = E.Engine(self.model, max_tokens=cache_tokens, max_slots=max_slots)
+        self.gen = torch.Generator().manual_seed(1)
+        say(f"{name}: {self.layers} layers, cache of {cache_tokens} tokens, ready in {time.time() - t0:.1f}s")
+        return self
 
     def __init__(self, sizes_name: str, layers: int, cache_tokens: int, max_slots: int):
         import torch
@@ -125,6 +192,7 @@ class Rig:
         self.layers = min(layers, self.layers_full) if layers > 0 else self.layers_full
         # the residual scale belongs to the full model whatever the number of layers run
         self.cfg = E.LlamaConfig(**sizes(sizes_name, num_hidden_layers=self.layers))
+        self.vocab = self.cfg.vocab_size
         dev = torch.device("cuda:0")
         t0 = time.time()
         plan = build_plan(self.cfg)
@@ -143,7 +211,7 @@ class Rig:
         self.torch.cuda.empty_cache()
 
     def prompts(self, n, length):
-        return [self.torch.randint(0, self.cfg.vocab_size, (length,), generator=self.gen).tolist() for _ in range(n)]
+        return [self.torch.randint(0, self.vocab, (length,), generator=self.gen).tolist() for _ in range(n)]
 
     def kv_bytes_per_token(self):
         return sum(g.bytes_per_token(2) for g in self.engine.cache.groups)
@@ -267,6 +335,41 @@ class Rig:
         return lens, best_pf, best_dec, kv
 
 
+def designs(args) -> int:
+    """``--only designs``: prefill and decode throughput of the Rigitar decoder beside the Llama-family decoder of
+    equal sizes; one JSON line."""
+    import torch
+    torch.cuda.set_device(0)
+    hbm_gbs, bf16_tf, peak_src = peaks()
+    B, C, T = args.batch, args.context, args.prefill_tokens
+    steps, warm = args.steps, max(3, args.warmup)
+    page = 64
+    room = (B + 1) * ((max(C, T) + page - 1) // page * page + page)
+    out = {"only": "designs", "batch": B, "context": C, "prefill_tokens": T, "steps": steps, "dtype": "bf16",
+           "data": "synthetic: random weights N(0,0.02), uniform random token ids", "peaks": peak_src, "sizes": {}}
+    for name in ([args.design_sizes] if args.design_sizes else sorted(DESIGN_SIZES)):
+        rig_cfg, llama_cfg = design_configs(name)
+        rec = {}
+        for arch, cfg in (("rigitar", rig_cfg), ("llama", llama_cfg)):
+            if args.design_arch not in ("both", arch):
+                continue
+            rig = Rig.of_config(f"{name}/{arch}", cfg, room, B + 1)
+            r = {"weight_bytes": rig.model.weight_bytes(), "cache_bytes_per_token": rig.kv_bytes_per_token()}
+            if args.design_part in ("both", "prefill"):
+                ms = rig.prefill(T, repeats=2)
+                r.update(prefill_ms=ms, prefill_tok_s=T / (ms / 1e3))
+            if args.design_part in ("both", "decode"):
+                ms, launches, kv = rig.decode(B, C, steps, warm)
+                gbs = (rig.model.weight_bytes() + kv) / (ms / steps / 1e3) / 1e9
+                r.update(decode_ms_per_step=ms / steps, decode_tok_s=B * steps / (ms / 1e3), decode_gb_s=gbs,
+                         decode_hbm_frac=gbs / hbm_gbs, gpu_launches_per_step=int(launches) // steps)
+            rec[arch] = r
+            rig.close()
+        out["sizes"][name] = rec
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     from exl3_server_b200.config.presets import SIZES
     ap = argparse.ArgumentParser()
@@ -281,8 +384,14 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip everything but the headline measurements")
     ap.add_argument("--sizes", choices=sorted(SIZES), default=HEADLINE,
                     help="layer sizes; other than the default only with --only (a short JSON line)")
-    ap.add_argument("--only", choices=["all", "decode", "prefill", "unequal"], default="all",
+    ap.add_argument("--only", choices=["all", "decode", "prefill", "unequal", "designs"], default="all",
                     help="run one part only (for profiling small cases); prints a short JSON line")
+    ap.add_argument("--design-sizes", choices=sorted(DESIGN_SIZES), default=None,
+                    help="with --only designs: one size pair instead of all")
+    ap.add_argument("--design-arch", choices=["both", "rigitar", "llama"], default="both",
+                    help="with --only designs: one of the two designs only")
+    ap.add_argument("--design-part", choices=["both", "prefill", "decode"], default="both",
+                    help="with --only designs: one of the two measurements only")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -293,6 +402,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.only == "designs":
+        return designs(args)
     if args.sizes != HEADLINE and args.only == "all":
         print(f"bench.py: --sizes other than {HEADLINE} needs --only decode, prefill or unequal")
         return 2

@@ -71,10 +71,11 @@ int exl3_attn_tokens_kv(const void* q, int64_t q_row_stride, void* out, int dtyp
 // exl3_attn_latent_row_tile: sixteens of rows a block takes for these sizes (0: dk does not fit shared memory).
 int exl3_attn_latent_row_tile(int dk, int max_rows);
 size_t exl3_attn_latent_scratch_bytes(int T, int H, int dv, int n_splits);
+// gate (float32 [T * H], or null): a factor per row on the output.
 int exl3_attn_latent(const void* q, void* out, const void* pool, const int* block_table, int bt_stride,
                      const int* row_start, const int* row_pos0, int B, int T, int max_new, int H, int dk, int dv, int page,
                      float scale, int pages_per_chunk, int n_splits, float* scratch, size_t scratch_bytes,
-                     cudaStream_t stream);
+                     const float* gate, cudaStream_t stream);
 
 // Residual update with the norm on the sublayer's output: h[t,:] += y[t,:] * rsqrt(mean(y[t,:]^2) + eps) * w (skipped
 // when y is null), then x[t,:] = h[t,:] in x_dtype (skipped when x is null).  Statistics and the sum are float32.
@@ -88,9 +89,12 @@ int exl3_xielu(const void* z, int z_dtype, const void* pq, int pq_dtype, void* o
 // minGRU over the packed tokens of a step.  zug [T, 3 * width]: the gate, candidate and output-gate projections
 // (biases added).  Per batch row b (tokens row_start[b] .. row_start[b + 1]) and channel, from state[slot_ids[b]]:
 // S = (1 - z) S + z c with z = sigmoid(zug[., 0:width]), c = u + 1/2 for u >= 0 else sigmoid(u), u = zug[., width:2 width];
-// y = S * silu(zug[., 2 width:]).  The last S goes back to the state.  All in float32.
+// y = S * silu(zug[., 2 width:]).  The last S goes back to the state.  All in float32.  max_new: the most tokens of
+// any row; rows of many tokens run as chunks side by side and need scratch (exl3_mingru_scratch_bytes; 0: none).
+size_t exl3_mingru_scratch_bytes(int B, int T, int width, int max_new);
 int exl3_mingru_scan(const void* zug, int zug_dtype, void* y, int y_dtype, float* state, const int* slot_ids,
-                     const int* row_start, int B, int T, int width, int max_new, cudaStream_t stream);
+                     const int* row_start, int B, int T, int width, int max_new, float* scratch, size_t scratch_bytes,
+                     cudaStream_t stream);
 
 // Latent attention, step 1, per token, from the joint projection a [T, lda] (float32 or bfloat16):
 //   cq [T, q_rank]      = rmsnorm(a[:, q_off : q_off + q_rank]) * wq
@@ -107,7 +111,8 @@ int exl3_latent_prep(const void* a, int a_dtype, int lda, int T, int q_off, int 
 // x[t, h, k] at x + t * x_row + h * x_head + k and out likewise; float32 sums in the order of k.  With rot_dim > 0 the
 // rot_dim features of x that follow a head's K are rotated (first rot of them, half-split pairs, at the token's
 // position) and written behind the head's outputs at out[t, h, tail_off ..]; what lies between N and tail_off and
-// behind the tail up to out_head is set to zero.  x, w and out have one element type.
+// behind the tail up to out_head is set to zero.  x, w and out have one element type.  With w null only the tails are
+// written (the products come from elsewhere).
 int exl3_head_gemm(const void* x, int64_t x_row, int x_head, const void* w, void* out, int64_t out_row, int out_head,
                    int dtype, int T, int heads, int K, int N, const float* mul, int rot_dim, int rot,
                    const float* inv_freq, const float* inv_freq_lo, const int* tok_pos, int tail_off,

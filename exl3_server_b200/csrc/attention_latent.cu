@@ -64,7 +64,7 @@ template <int MT>
 __global__ void __launch_bounds__(LA_THREADS, 1)
 attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat16* pool, const int* __restrict__ block_table,
                    int bt_stride, const int* __restrict__ row_start, const int* __restrict__ row_pos0, int H, int dk, int dv,
-                   float scale_log2, int pages_per_chunk, int n_splits, float* scratch) {
+                   float scale_log2, int pages_per_chunk, int n_splits, float* scratch, const float* gate) {
   constexpr int M = 16 * MT;
   extern __shared__ __align__(16) unsigned char la_smem[];
   const int ldk = dk + LA_PAD;                      // elements per shared-memory row of Q and K
@@ -145,19 +145,39 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
     const __nv_bfloat16* Kt = Ks + (size_t)buf * LA_KEYS * ldk;
 
     // scores of all rows against this warp's 8 keys
-    float s[MT][4];
+    // (with few row tiles the features go round KS sums per tile, so that the chain of dependent products is short)
+    constexpr int KS = MT >= 4 ? 1 : 4 / MT;
+    float sk[MT][KS][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) { s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.0f; }
-    for (int k0 = 0; k0 < dk; k0 += 16) {
-      uint32_t bf[2];
-      la_ldmatrix_x2(bf, Kt + (size_t)bk_row * ldk + k0 + bk_col);
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        uint32_t af[4];
-        la_ldmatrix_x4(af, Qs + (size_t)(mt * 16 + a_row) * ldk + k0 + a_col);
-        la_mma(s[mt], af, bf[0], bf[1]);
+      for (int u = 0; u < KS; ++u) { sk[mt][u][0] = sk[mt][u][1] = sk[mt][u][2] = sk[mt][u][3] = 0.0f; }
+    for (int k0 = 0; k0 < dk; k0 += 16 * KS) {
+#pragma unroll
+      for (int u = 0; u < KS; ++u) {
+        const int kk = k0 + 16 * u;
+        if (kk < dk) {
+          uint32_t bf[2];
+          la_ldmatrix_x2(bf, Kt + (size_t)bk_row * ldk + kk + bk_col);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            uint32_t af[4];
+            la_ldmatrix_x4(af, Qs + (size_t)(mt * 16 + a_row) * ldk + kk + a_col);
+            la_mma(sk[mt][u], af, bf[0], bf[1]);
+          }
+        }
       }
     }
+    float s[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = sk[mt][0][e];
+#pragma unroll
+        for (int u = 1; u < KS; ++u) v += sk[mt][u][e];
+        s[mt][e] = v;
+      }
     const int key0 = pi * LA_KEYS + warp * 8 + qc;           // this lane's first key (absolute position)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
@@ -255,7 +275,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
       const int64_t flat = (int64_t)tok0 * H + f0 + r;
       const float l = l_run[r], mx = m_run[r];
       if (n_splits <= 1) {
-        const float inv = 1.0f / l;
+        const float inv = (gate ? __ldcg(gate + flat) : 1.0f) / l;
 #pragma unroll
         for (int i = 0; i < LA_MAX_PAIRS; ++i) {
           const int col = (warp + LA_WARPS * i) * 16;
@@ -289,7 +309,10 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
 // out = sum_s acc_s w_s / sum_s l_s w_s, both in chunk order.  A block that found no key for a row in its chunk
 // (or that had no tile to work on) left nothing: such records are told by the chunk's first key lying beyond the row.
 __global__ void latent_combine_kernel(const float* __restrict__ scratch, __nv_bfloat16* out, const int* __restrict__ row_start,
-                                      const int* __restrict__ row_pos0, int H, int dv, int n_splits, int pages_per_chunk) {
+                                      const int* __restrict__ row_pos0, int H, int dv, int n_splits, int pages_per_chunk,
+                                      const float* gate) {
+  extern __shared__ float wsm[];                     // [n_splits] weights
+  __shared__ float inv_l;
   pdl_wait();
   pdl_trigger();
   const int b = blockIdx.y;
@@ -302,14 +325,24 @@ __global__ void latent_combine_kernel(const float* __restrict__ scratch, __nv_bf
   const int64_t flat = (int64_t)tok0 * H + f;
   const int rec = dv + 2;
   const float* base = scratch + flat * n_splits * rec;
+  for (int s = threadIdx.x; s < used; s += blockDim.x) wsm[s] = __ldcg(base + (int64_t)s * rec + dv);
+  __syncthreads();
   float mx = -INFINITY;
-  for (int s = 0; s < used; ++s) mx = fmaxf(mx, __ldcg(base + (int64_t)s * rec + dv));
-  float ll = 0.0f;
-  for (int s = 0; s < used; ++s) ll += __ldcg(base + (int64_t)s * rec + dv + 1) * la_exp2(__ldcg(base + (int64_t)s * rec + dv) - mx);
+  for (int s = 0; s < used; ++s) mx = fmaxf(mx, wsm[s]);
+  __syncthreads();
+  for (int s = threadIdx.x; s < used; s += blockDim.x) wsm[s] = la_exp2(wsm[s] - mx);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ll = 0.0f;
+    for (int s = 0; s < used; ++s) ll += __ldcg(base + (int64_t)s * rec + dv + 1) * wsm[s];
+    inv_l = (gate ? __ldcg(gate + flat) : 1.0f) / ll;
+  }
+  __syncthreads();
   for (int d = threadIdx.x; d < dv; d += blockDim.x) {
     float aa = 0.0f;
-    for (int s = 0; s < used; ++s) aa += __ldcg(base + (int64_t)s * rec + d) * la_exp2(__ldcg(base + (int64_t)s * rec + dv) - mx);
-    out[flat * dv + d] = __float2bfloat16_rn(aa / ll);
+#pragma unroll 4
+    for (int s = 0; s < used; ++s) aa += __ldcg(base + (int64_t)s * rec + d) * wsm[s];
+    out[flat * dv + d] = __float2bfloat16_rn(aa * inv_l);
   }
 }
 
@@ -322,7 +355,7 @@ static size_t la_smem_bytes(int MT, int dk) {
 template <int MT>
 static int la_launch(const void* q, void* out, const void* pool, const int* block_table, int bt_stride, const int* row_start,
                      const int* row_pos0, int B, int max_rows, int H, int dk, int dv, float scale, int pages_per_chunk,
-                     int n_splits, float* scratch, cudaStream_t stream) {
+                     int n_splits, float* scratch, const float* gate, cudaStream_t stream) {
   const size_t smem = la_smem_bytes(MT, dk);
   cudaError_t e = cudaFuncSetAttribute(attn_latent_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
@@ -332,7 +365,7 @@ static int la_launch(const void* q, void* out, const void* pool, const int* bloc
   dim3 grid(B, ceil_div(max_rows, 16 * MT), n_splits);
   launch_pdl(attn_latent_kernel<MT>, grid, dim3(LA_THREADS), smem, stream, static_cast<const __nv_bfloat16*>(q),
              static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(pool), block_table, bt_stride, row_start,
-             row_pos0, H, dk, dv, scale * 1.4426950408889634f, pages_per_chunk, n_splits, scratch);
+             row_pos0, H, dk, dv, scale * 1.4426950408889634f, pages_per_chunk, n_splits, scratch, gate);
   return launch_status("attn_latent");
 }
 
@@ -355,7 +388,7 @@ extern "C" size_t exl3_attn_latent_scratch_bytes(int T, int H, int dv, int n_spl
 extern "C" int exl3_attn_latent(const void* q, void* out, const void* pool, const int* block_table, int bt_stride,
                                 const int* row_start, const int* row_pos0, int B, int T, int max_new, int H, int dk, int dv,
                                 int page, float scale, int pages_per_chunk, int n_splits, float* scratch,
-                                size_t scratch_bytes, cudaStream_t stream) {
+                                size_t scratch_bytes, const float* gate, cudaStream_t stream) {
   if (B == 0 || T == 0) return 0;
   if (B < 0 || T < 0 || max_new < 1 || H < 1 || dk < 16 || dk % 16 != 0 || dv < 16 || dv % 16 != 0 || dv > dk ||
       dv > LA_WARPS * LA_MAX_PAIRS * 16 || page != LA_KEYS || n_splits < 1 || n_splits > 65535 ||
@@ -377,15 +410,16 @@ extern "C" int exl3_attn_latent(const void* q, void* out, const void* pool, cons
   const int max_rows = (int)max_rows64;
   const int mt = exl3_attn_latent_row_tile(dk, max_rows);
   int rc;
-  if (mt == 4) rc = la_launch<4>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, stream);
-  else if (mt == 2) rc = la_launch<2>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, stream);
-  else if (mt == 1) rc = la_launch<1>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, stream);
+  if (mt == 4) rc = la_launch<4>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
+  else if (mt == 2) rc = la_launch<2>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
+  else if (mt == 1) rc = la_launch<1>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
   else { set_error("attn_latent: rows of %d features do not fit shared memory", dk); return ERR_UNSUPPORTED; }
   if (rc) return rc;
   if (n_splits > 1) {
     if (B > 65535) { set_error("attn_latent: too many sequences for the merge"); return ERR_UNSUPPORTED; }
-    launch_pdl(latent_combine_kernel, dim3(max_rows, B), dim3(128), 0, stream, (const float*)scratch,
-               static_cast<__nv_bfloat16*>(out), row_start, row_pos0, H, dv, n_splits, pages_per_chunk);
+    launch_pdl(latent_combine_kernel, dim3(max_rows, B), dim3(128), (size_t)n_splits * sizeof(float), stream,
+               (const float*)scratch, static_cast<__nv_bfloat16*>(out), row_start, row_pos0, H, dv, n_splits,
+               pages_per_chunk, gate);
     rc = launch_status("latent_combine");
   }
   return rc;

@@ -92,16 +92,22 @@ latent_prep_kernel(const void* a, int a_dtype, int lda, int q_off, int q_rank, c
 }
 
 constexpr int HG_TM = 8;          // tokens per block
-constexpr int HG_TN = 128;        // outputs per block, one per thread
-constexpr int HG_KC = 64;         // features of x staged at a time
+constexpr int HG_TN = 32;         // outputs per block: a warp's lanes
+constexpr int HG_KG = 8;          // warps of a block; each takes every eighth slice of a staged piece of K
+constexpr int HG_KC = 256;        // features of x staged at a time
 
+// A block takes 8 tokens x 32 outputs of one head.  Its eight warps split the features k between them (a warp's
+// lanes read 32 consecutive outputs of one row of w: one 64- or 128-byte piece), so a token's step, which has one
+// block of tokens, still has (N / 32) * heads blocks of 256 threads with K / 8 loads each in flight, and the
+// partial sums meet in shared memory in the order of the warps.
 template <typename T>
-__global__ void __launch_bounds__(HG_TN)
+__global__ void __launch_bounds__(HG_TN * HG_KG)
 head_gemm_kernel(const T* x, int64_t x_row, int x_head, const T* __restrict__ w, T* out, int64_t out_row, int out_head,
                  int Tn, int heads, int K, int N, const float* mul, int rot_dim, int rot,
                  const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo,
                  const int* __restrict__ tok_pos, int tail_off, int n_blocks) {
   __shared__ float xs[HG_TM][HG_KC];
+  __shared__ float part[HG_KG][HG_TM][HG_TN];
   pdl_wait();
   pdl_trigger();
   const int h = blockIdx.z, t0 = blockIdx.y * HG_TM;
@@ -130,7 +136,8 @@ head_gemm_kernel(const T* x, int64_t x_row, int x_head, const T* __restrict__ w,
     }
     return;
   }
-  const int n = blockIdx.x * HG_TN + threadIdx.x;
+  const int lane = threadIdx.x & 31, kg = threadIdx.x >> 5;
+  const int n = blockIdx.x * HG_TN + lane;
   float acc[HG_TM];
 #pragma unroll
   for (int m = 0; m < HG_TM; ++m) acc[m] = 0.0f;
@@ -144,21 +151,35 @@ head_gemm_kernel(const T* x, int64_t x_row, int x_head, const T* __restrict__ w,
     __syncthreads();
     if (n < N) {
       const int kc = min(HG_KC, K - k0);
-      for (int k = 0; k < kc; ++k) {
+      // this warp's features of the piece: kg, kg + 8, ...  (four loads in flight)
+      int k = kg;
+      for (; k + 3 * HG_KG < kc; k += 4 * HG_KG) {
+        float wv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) wv[u] = Elem<T>::load(wh + (int64_t)(k0 + k + u * HG_KG) * N + n);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int m = 0; m < HG_TM; ++m) acc[m] = fmaf(xs[m][k + u * HG_KG], wv[u], acc[m]);
+      }
+      for (; k < kc; k += HG_KG) {
         const float wv = Elem<T>::load(wh + (int64_t)(k0 + k) * N + n);
 #pragma unroll
         for (int m = 0; m < HG_TM; ++m) acc[m] = fmaf(xs[m][k], wv, acc[m]);
       }
     }
   }
-  if (n < N) {
 #pragma unroll
-    for (int m = 0; m < HG_TM; ++m) {
-      const int t = t0 + m;
-      if (t < Tn) {
-        const float f = mul ? __ldcg(mul + (int64_t)t * heads + h) : 1.0f;
-        Elem<T>::store(out + (int64_t)t * out_row + (int64_t)h * out_head + n, acc[m] * f);
-      }
+  for (int m = 0; m < HG_TM; ++m) part[kg][m][lane] = acc[m];
+  __syncthreads();
+  {
+    const int m = kg, t = t0 + m;                      // warp m adds up token m's partial sums, in the order of the warps
+    if (n < N && t < Tn) {
+      float sum = 0.0f;
+#pragma unroll
+      for (int g = 0; g < HG_KG; ++g) sum += part[g][m][lane];
+      const float f = mul ? __ldcg(mul + (int64_t)t * heads + h) : 1.0f;
+      Elem<T>::store(out + (int64_t)t * out_row + (int64_t)h * out_head + n, sum * f);
     }
   }
 }
@@ -199,9 +220,10 @@ extern "C" int exl3_head_gemm(const void* x, int64_t x_row, int x_head, const vo
               out_head, rot_dim, rot, tail_off);
     return ERR_BAD_ARGUMENT;
   }
-  const int n_blocks = ceil_div(N, HG_TN);
+  const int n_blocks = w == nullptr ? 0 : ceil_div(N, HG_TN);     // no weights: only the tails are written
   const int tail = out_head > N ? 1 : 0;
   const int rows = ceil_div(T, HG_TM);
+  if (n_blocks + tail == 0) return 0;
   if (rows > 65535) {
     // grid.y is limited: walk the tokens in slabs
     const int slab = 65535 * HG_TM;
@@ -218,11 +240,11 @@ extern "C" int exl3_head_gemm(const void* x, int64_t x_row, int x_head, const vo
   }
   dim3 grid(n_blocks + tail, rows, heads);
   if (dtype == DT_F32) {
-    launch_pdl(head_gemm_kernel<float>, grid, dim3(HG_TN), 0, stream, static_cast<const float*>(x), x_row, x_head,
+    launch_pdl(head_gemm_kernel<float>, grid, dim3(HG_TN * HG_KG), 0, stream, static_cast<const float*>(x), x_row, x_head,
                static_cast<const float*>(w), static_cast<float*>(out), out_row, out_head, T, heads, K, N, mul, rot_dim, rot,
                inv_freq, inv_freq_lo, tok_pos, tail_off, n_blocks);
   } else if (dtype == DT_BF16) {
-    launch_pdl(head_gemm_kernel<__nv_bfloat16>, grid, dim3(HG_TN), 0, stream, static_cast<const __nv_bfloat16*>(x), x_row,
+    launch_pdl(head_gemm_kernel<__nv_bfloat16>, grid, dim3(HG_TN * HG_KG), 0, stream, static_cast<const __nv_bfloat16*>(x), x_row,
                x_head, static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(out), out_row, out_head, T, heads,
                K, N, mul, rot_dim, rot, inv_freq, inv_freq_lo, tok_pos, tail_off, n_blocks);
   } else {

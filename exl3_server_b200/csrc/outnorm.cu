@@ -69,6 +69,62 @@ norm_add_kernel(float* h, const void* y, int y_dtype, const void* __restrict__ w
   }
 }
 
+// Eight consecutive values as floats, from float32 or bfloat16 storage (p 16-byte aligned for bfloat16, 32 for float32).
+__device__ inline void on_load8(const float* p, float (&v)[8], bool through_l2) {
+  float a[4], b[4];
+  if (through_l2) { load_vec_cg(p, a); load_vec_cg(p + 4, b); } else { load_vec(p, a); load_vec(p + 4, b); }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { v[e] = a[e]; v[4 + e] = b[e]; }
+}
+__device__ inline void on_load8(const __nv_bfloat16* p, float (&v)[8], bool through_l2) {
+  if (through_l2) load_vec_cg(p, v); else load_vec(p, v);
+}
+__device__ inline void on_store8(float* p, const float (&v)[8]) {
+  const float a[4] = {v[0], v[1], v[2], v[3]}, b[4] = {v[4], v[5], v[6], v[7]};
+  store_vec(p, a);
+  store_vec(p + 4, b);
+}
+__device__ inline void on_store8(__nv_bfloat16* p, const float (&v)[8]) { store_vec(p, v); }
+
+constexpr int NA_VECS = 4;                       // pieces of 8 values per thread: rows up to 8192
+
+// The same for rows of up to NA_THREADS * 8 * NA_VECS values, a multiple of 8: a thread keeps its pieces of y in
+// registers and every access is 16 or 32 bytes wide.  TX void: no copy of the residual is written.
+template <typename TY, typename TW, typename TX>
+__global__ void __launch_bounds__(NA_THREADS)
+norm_add_vec_kernel(float* h, const TY* y, const TW* __restrict__ w, float eps, TX* x, int H) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int64_t base = (int64_t)blockIdx.x * H;
+  float keep[NA_VECS][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int p = 0; p < NA_VECS; ++p) {
+    const int c = (p * NA_THREADS + threadIdx.x) * 8;
+    if (c < H) {
+      on_load8(y + base + c, keep[p], true);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += keep[p][e] * keep[p][e];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int p = 0; p < NA_VECS; ++p) {
+    const int c = (p * NA_THREADS + threadIdx.x) * 8;
+    if (c < H) {
+      float hv[8], wv[8];
+      on_load8(h + base + c, hv, true);
+      on_load8(w + c, wv, false);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) hv[e] += keep[p][e] * inv * wv[e];
+      on_store8(h + base + c, hv);
+      if (x) on_store8(x + base + c, hv);
+    }
+  }
+}
+
 __device__ inline float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 
 __global__ void xielu_kernel(const void* z, int z_dtype, const void* __restrict__ pq, int pq_dtype, void* out,
@@ -84,6 +140,32 @@ __global__ void xielu_kernel(const void* z, int z_dtype, const void* __restrict_
   }
 }
 
+template <typename TI, typename TO>
+__global__ void xielu_vec_kernel(const TI* z, const void* __restrict__ pq, int pq_dtype, TO* out, int64_t n8) {
+  pdl_wait();
+  pdl_trigger();
+  const float ap = softplus_f(on_load_any(pq, pq_dtype, 0));
+  const float an = 0.5f + softplus_f(on_load_any(pq, pq_dtype, 1));
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    float v[8];
+    on_load8(z + i * 8, v, true);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = v[e] > 0.0f ? fmaf(ap * v[e], v[e], 0.5f * v[e]) : fmaf(an, expm1f(v[e]) - v[e], 0.5f * v[e]);
+    on_store8(out + i * 8, v);
+  }
+}
+
+template <typename TY, typename TW>
+static void norm_add_vec(float* h, const void* y, const void* w, float eps, void* x, int x_dtype, int T, int H,
+                         cudaStream_t stream) {
+  if (x == nullptr || x_dtype == DT_F32)
+    launch_pdl(norm_add_vec_kernel<TY, TW, float>, dim3(T), dim3(NA_THREADS), 0, stream, h, static_cast<const TY*>(y),
+               static_cast<const TW*>(w), eps, static_cast<float*>(x), H);
+  else
+    launch_pdl(norm_add_vec_kernel<TY, TW, __nv_bfloat16>, dim3(T), dim3(NA_THREADS), 0, stream, h,
+               static_cast<const TY*>(y), static_cast<const TW*>(w), eps, static_cast<__nv_bfloat16*>(x), H);
+}
+
 }  // namespace exl3
 
 using namespace exl3;
@@ -95,7 +177,13 @@ extern "C" int exl3_norm_add(float* h, const void* y, int y_dtype, const void* w
     set_error("norm_add: bad arguments T=%d H=%d", T, H);
     return ERR_BAD_ARGUMENT;
   }
-  launch_pdl(norm_add_kernel, dim3(T), dim3(NA_THREADS), 0, stream, h, y, y_dtype, w, w_dtype, eps, x, x_dtype, H);
+  const bool vec = y != nullptr && H % 8 == 0 && H <= NA_THREADS * 8 * NA_VECS && aligned16(h) && aligned16(y) &&
+                   aligned16(w) && aligned16(x);
+  if (vec && y_dtype == DT_BF16 && w_dtype == DT_BF16) norm_add_vec<__nv_bfloat16, __nv_bfloat16>(h, y, w, eps, x, x_dtype, T, H, stream);
+  else if (vec && y_dtype == DT_F32 && w_dtype == DT_BF16) norm_add_vec<float, __nv_bfloat16>(h, y, w, eps, x, x_dtype, T, H, stream);
+  else if (vec && y_dtype == DT_BF16 && w_dtype == DT_F32) norm_add_vec<__nv_bfloat16, float>(h, y, w, eps, x, x_dtype, T, H, stream);
+  else if (vec && y_dtype == DT_F32 && w_dtype == DT_F32) norm_add_vec<float, float>(h, y, w, eps, x, x_dtype, T, H, stream);
+  else launch_pdl(norm_add_kernel, dim3(T), dim3(NA_THREADS), 0, stream, h, y, y_dtype, w, w_dtype, eps, x, x_dtype, H);
   return launch_status("norm_add");
 }
 
@@ -103,6 +191,21 @@ extern "C" int exl3_xielu(const void* z, int z_dtype, const void* pq, int pq_dty
                           int64_t n, cudaStream_t stream) {
   if (n == 0) return 0;
   if (n < 0) { set_error("xielu: bad size"); return ERR_BAD_ARGUMENT; }
+  if (n % 8 == 0 && aligned16(z) && aligned16(out)) {
+    const int64_t n8 = n / 8;
+    int64_t blocks = (n8 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    const dim3 g((unsigned)blocks), t(256);
+    if (z_dtype == DT_F32 && out_dtype == DT_BF16)
+      launch_pdl(xielu_vec_kernel<float, __nv_bfloat16>, g, t, 0, stream, static_cast<const float*>(z), pq, pq_dtype, static_cast<__nv_bfloat16*>(out), n8);
+    else if (z_dtype == DT_BF16 && out_dtype == DT_BF16)
+      launch_pdl(xielu_vec_kernel<__nv_bfloat16, __nv_bfloat16>, g, t, 0, stream, static_cast<const __nv_bfloat16*>(z), pq, pq_dtype, static_cast<__nv_bfloat16*>(out), n8);
+    else if (z_dtype == DT_F32 && out_dtype == DT_F32)
+      launch_pdl(xielu_vec_kernel<float, float>, g, t, 0, stream, static_cast<const float*>(z), pq, pq_dtype, static_cast<float*>(out), n8);
+    else
+      launch_pdl(xielu_vec_kernel<__nv_bfloat16, float>, g, t, 0, stream, static_cast<const __nv_bfloat16*>(z), pq, pq_dtype, static_cast<float*>(out), n8);
+    return launch_status("xielu");
+  }
   int64_t blocks = (n + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
   launch_pdl(xielu_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, z, z_dtype, pq, pq_dtype, out, out_dtype, n);

@@ -40,6 +40,12 @@ class Workspace:
             self._buf = torch.zeros(max(n, 1 << 16), dtype=torch.float32, device=self.device)
         return self._buf
 
+    COUNTERS = 65536      # floats at the buffer's start that the CUDA-core attention keeps as counters (zero between launches)
+
+    def plain(self, n: int) -> torch.Tensor:
+        """``n`` floats of scratch for kernels that write what they like: the buffer's part behind the counters."""
+        return self.floats(n + self.COUNTERS)[self.COUNTERS:]
+
     def reserve(self, n: int) -> None:
         self.floats(n)
 

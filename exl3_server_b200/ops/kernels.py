@@ -516,7 +516,7 @@ def attn_latent_scratch_bytes(T: int, heads: int, dv: int, n_splits: int) -> int
 def attn_latent(q: torch.Tensor, out: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
                 row_start: torch.Tensor, row_pos0: torch.Tensor, rows: int, T: int, max_new: int, heads: int, dk: int,
                 dv: int, page: int, scale: float, pages_per_chunk: int, n_splits: int,
-                scratch: Optional[torch.Tensor]) -> torch.Tensor:
+                scratch: Optional[torch.Tensor], gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of a step's tokens over latent rows on the tensor cores (see attention_latent.cu): ``q [T, heads *
     dk]``, ``out [T, heads * dv]``, one cached row of ``dk`` features per key whose first ``dv`` are the values."""
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16:
@@ -527,8 +527,8 @@ def attn_latent(q: torch.Tensor, out: torch.Tensor, pool: torch.Tensor, block_ta
     _check(library().exl3_attn_latent(
         _ptr(q), _ptr(out), _ptr(pool), _ptr(block_table), _c_int(block_table.stride(0)), _ptr(row_start),
         _ptr(row_pos0), _c_int(rows), _c_int(T), _c_int(max_new), _c_int(heads), _c_int(dk), _c_int(dv), _c_int(page),
-        _c_float(scale), _c_int(pages_per_chunk), _c_int(n_splits), _ptr(scratch), _c_size_t(nbytes), _stream()),
-        "attn_latent")
+        _c_float(scale), _c_int(pages_per_chunk), _c_int(n_splits), _ptr(scratch), _c_size_t(nbytes), _ptr(gate),
+        _stream()), "attn_latent")
     return out
 
 
@@ -565,8 +565,15 @@ def xielu(z: torch.Tensor, pq: torch.Tensor, out_dtype: torch.dtype) -> torch.Te
     return out
 
 
+def mingru_scratch_bytes(rows: int, T: int, width: int, max_new: int) -> int:
+    lib = library()
+    lib.exl3_mingru_scratch_bytes.restype = _c_size_t
+    return int(lib.exl3_mingru_scratch_bytes(_c_int(rows), _c_int(T), _c_int(width), _c_int(max_new)))
+
+
 def mingru_scan(zug: torch.Tensor, state: torch.Tensor, slot_ids: torch.Tensor, row_start: torch.Tensor,
-                rows: int, width: int, max_new: int, out_dtype: torch.dtype) -> torch.Tensor:
+                rows: int, width: int, max_new: int, out_dtype: torch.dtype,
+                scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The minGRU recurrence over a step's packed tokens (see recurrent.cu): ``zug [T, 3 * width]``, ``state
     [slots, width]`` float32 read and written at ``slot_ids``; returns ``S_t * silu(g_t)`` as ``[T, width]``."""
     T = zug.shape[0]
@@ -579,7 +586,9 @@ def mingru_scan(zug: torch.Tensor, state: torch.Tensor, slot_ids: torch.Tensor, 
     y = torch.empty((T, width), dtype=out_dtype, device=zug.device)
     _check(library().exl3_mingru_scan(_ptr(zug), _c_int(dtype_code(zug.dtype)), _ptr(y), _c_int(dtype_code(y.dtype)),
                                       _ptr(state), _ptr(slot_ids), _ptr(row_start), _c_int(rows), _c_int(T),
-                                      _c_int(width), _c_int(max_new), _stream()), "mingru_scan")
+                                      _c_int(width), _c_int(max_new), _ptr(scratch),
+                                      _c_size_t(0 if scratch is None else scratch.numel() * scratch.element_size()),
+                                      _stream()), "mingru_scan")
     return y
 
 
@@ -606,15 +615,19 @@ def latent_prep(a: torch.Tensor, q_off: int, q_rank: int, wq: torch.Tensor, kv_o
     return cq, gate
 
 
-def head_gemm(x: torch.Tensor, x_row: int, x_head: int, w: torch.Tensor, out: torch.Tensor, out_row: int,
+def head_gemm(x: torch.Tensor, x_row: int, x_head: int, w: Optional[torch.Tensor], out: torch.Tensor, out_row: int,
               out_head: int, T: int, heads: int, K: int, N: int, mul: Optional[torch.Tensor] = None, rot_dim: int = 0,
               rot: int = 0, inv_freq: Optional[torch.Tensor] = None, tok_pos: Optional[torch.Tensor] = None,
               tail_off: int = 0) -> torch.Tensor:
     """``out[t, h, n] = mul[t, h] * sum_k x[t, h, k] w[h, k, n]`` with the given row and head pitches (elements);
-    with ``rot_dim`` the features behind a head's ``K`` are rotated and written at ``tail_off`` (see latent.cu)."""
-    if w.dtype != x.dtype or out.dtype != x.dtype or tuple(w.shape) != (heads, K, N):
-        raise KernelLibraryError(f"head_gemm: w {tuple(w.shape)} must be {(heads, K, N)} in the type of x and out")
-    _contig(w, "w")
+    with ``rot_dim`` the features behind a head's ``K`` are rotated and written at ``tail_off`` (see latent.cu).  With
+    ``w`` None only those tails (and the zeros around them) are written."""
+    if w is not None:
+        if w.dtype != x.dtype or tuple(w.shape) != (heads, K, N):
+            raise KernelLibraryError(f"head_gemm: w {tuple(w.shape)} must be {(heads, K, N)} in the type of x and out")
+        _contig(w, "w")
+    if out.dtype != x.dtype:
+        raise KernelLibraryError("head_gemm: x and out differ in element type")
     f_hi, f_lo = (_rotary_rows(inv_freq, rot, "head_gemm") if rot > 0 and inv_freq is not None
                   else (_c_void_p(0), _c_void_p(0)))
     _check(library().exl3_head_gemm(

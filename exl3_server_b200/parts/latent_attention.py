@@ -37,8 +37,11 @@ from .position import RotaryPosition
 from .registry import register_mixer
 from .spec import MixerSpec, PositionSpec
 
-# Keys per work item of the attention kernel; a multiple of the cache's page size.
+# Keys per work item of the CUDA-core attention kernel; a multiple of the cache's page size.
 SPLIT_KEYS = 256
+# Tokens in a step beyond which the bfloat16 products per head (queries into the latent space, values out of it) are
+# the library's batched product; up to here this library's kernel, which reads the weights once.
+MANY_ROWS = 64
 
 
 def _up16(n: int) -> int:
@@ -129,29 +132,41 @@ class LatentAttention:
                                  self.rank_pad, dt)
         q = self.uq(cq)                                                   # [T, H * (dim + rot_dim)]
         hq = self.dim + self.rot_dim
+        many = dt == torch.bfloat16 and T > MANY_ROWS                     # the per-head products go to the library
         ql = torch.empty((T, H * self.row), dtype=dt, device=x.device)    # per head [q^n Wuk | 0 | rope(q^r) | 0]
-        K.head_gemm(q, H * hq, hq, self.w_uk, ql, H * self.row, self.row, T, H, self.dim, self.kv_rank,
-                    rot_dim=self.rot_dim, rot=self.rot, inv_freq=self.inv_freq, tok_pos=batch.tok_pos,
+        K.head_gemm(q, H * hq, hq, None if many else self.w_uk, ql, H * self.row, self.row, T, H, self.dim,
+                    self.kv_rank, rot_dim=self.rot_dim, rot=self.rot, inv_freq=self.inv_freq, tok_pos=batch.tok_pos,
                     tail_off=self.rank_pad)
+        if many:
+            ql.view(T, H, self.row)[:, :, :self.kv_rank] = torch.bmm(
+                q.view(T, H, hq)[:, :, :self.dim].transpose(0, 1), self.w_uk).transpose(0, 1)
         ol = torch.empty((T, H * self.rank_pad), dtype=dt, device=x.device)
-        self.attend(ql, ol, batch, kv)
-        o = torch.empty((T, H * self.vdim), dtype=dt, device=x.device)
-        K.head_gemm(ol, H * self.rank_pad, self.rank_pad, self.w_uv, o, H * self.vdim, self.vdim, T, H, self.kv_rank,
-                    self.vdim, mul=gate)
+        gated = self.attend(ql, ol, batch, kv, gate)
+        if many:
+            o = torch.bmm(ol.view(T, H, self.rank_pad)[:, :, :self.kv_rank].transpose(0, 1), self.w_uv)
+            o = o.transpose(0, 1).reshape(T, H * self.vdim)
+            if not gated:
+                o = (o.view(T, H, self.vdim) * gate[:, :, None]).to(dt).view(T, H * self.vdim)
+        else:
+            o = torch.empty((T, H * self.vdim), dtype=dt, device=x.device)
+            K.head_gemm(ol, H * self.rank_pad, self.rank_pad, self.w_uv, o, H * self.vdim, self.vdim, T, H,
+                        self.kv_rank, self.vdim, mul=None if gated else gate)
         return self.o(o, out_dtype=self.o.wide_dtype(T))
 
-    def attend(self, ql: torch.Tensor, ol: torch.Tensor, batch, kv) -> None:
-        """Attention of the step's tokens over the cached rows: ``H`` query heads on one row per key."""
+    def attend(self, ql: torch.Tensor, ol: torch.Tensor, batch, kv, gate: torch.Tensor) -> bool:
+        """Attention of the step's tokens over the cached rows: ``H`` query heads on one row per key.  Returns
+        whether the gate is already in ``ol`` (a factor per (token, head) commutes with the head's value projection,
+        and the tensor-core kernel applies it as it writes)."""
         T = ql.shape[0]
         if K.attn_latent_supported(ql.dtype, self.row, self.rank_pad, kv.page_size):
             # bfloat16: both products on the tensor cores, a block per tile of a sequence's (token, head) rows
             per, n = self._chunks(batch, kv.page_size, ql.device)
             scratch = None
             if n > 1:
-                scratch = batch.workspace.floats(K.attn_latent_scratch_bytes(T, self.H, self.rank_pad, n) // 4)
+                scratch = batch.workspace.plain(K.attn_latent_scratch_bytes(T, self.H, self.rank_pad, n) // 4)
             K.attn_latent(ql, ol, kv.k, kv.block_table, batch.row_start, batch.row_pos0, batch.n_rows, T, batch.max_new,
-                          self.H, self.row, self.rank_pad, kv.page_size, self.scale, per, n, scratch)
-            return
+                          self.H, self.row, self.rank_pad, kv.page_size, self.scale, per, n, scratch, gate)
+            return True
         split = max(SPLIT_KEYS, kv.page_size)
         if split % kv.page_size:
             split = kv.page_size * (split // kv.page_size + 1)
@@ -161,17 +176,18 @@ class LatentAttention:
             scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, self.H, self.rank_pad, n) // 4)
         K.attn_tokens_kv(ql, ql.stride(0), ol, kv.k, kv.k, kv.block_table, batch.tok_pos, batch.tok_seq, T, self.H, 1,
                          self.row, self.rank_pad, self.row, kv.page_size, 0, self.scale, split, n, scratch)
+        return False
 
     def _chunks(self, batch, page: int, device):
         """``(pages per chunk, chunks)`` for the tensor-core kernel: one chunk when the step's tiles of rows already
         give every SM a block (prompts, large batches); else the keys are cut into as many chunks of whole pages as
-        it takes to get there, none shorter than four pages.  The choice depends on the step's size, not on a token's
+        it takes to get there, none shorter than two pages.  The choice depends on the step's size, not on a token's
         position: results differ between batch sizes by rounding."""
         pages = max(1, (batch.max_kv_len + page - 1) // page)
         tile = K.attn_latent_row_tile(self.row, batch.max_new * self.H)
         blocks = batch.n_rows * ((batch.max_new * self.H + tile - 1) // tile)
         want = max(1, K.sm_count(device) // max(1, blocks))
-        n = max(1, min(want, pages // 4))
+        n = max(1, min(want, pages // 2))
         per = (pages + n - 1) // n
         return per, (pages + per - 1) // per
 

@@ -11,7 +11,8 @@
 The state starts at zero (the cache zeroes a slot's row when it is opened), is
 float32 and is carried from step to step in the cache's per-sequence state, so a
 prompt cut into steps in any way, and token-by-token decoding, walk the same
-chain of sums.  The three input projections are one matrix; the gates, the
+chain of sums (rows of many tokens are cut into chunks that run side by side and
+are joined through the recurrence's linearity, which changes roundings only).  The three input projections are one matrix; the gates, the
 candidate and the recurrence are float32 (``csrc/recurrent.cu``).
 
 Tensor names under the mixer's prefix: ``z``, ``z.b``, ``x``, ``x.b``, ``g``, ``o``.
@@ -68,8 +69,10 @@ class MinGRU:
         if state is None:
             raise RuntimeError("mingru needs its per-sequence state")
         zug = self.zug(x, out_dtype=self.zug.wide_dtype(x.shape[0]))
+        need = K.mingru_scratch_bytes(batch.n_rows, x.shape[0], self.inner, batch.max_new)
+        scratch = batch.workspace.plain(need // 4) if need else None      # prompts: chunks side by side
         y = K.mingru_scan(zug, state, batch.slot_ids, batch.row_start, batch.n_rows, self.inner, batch.max_new,
-                          self.ctx.dtype)
+                          self.ctx.dtype, scratch)
         return self.o(y, out_dtype=self.o.wide_dtype(x.shape[0]))
 
     def weight_bytes(self) -> int:
