@@ -97,18 +97,25 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
   const int* bt = block_table + (int64_t)b * bt_stride;
   const int vecs = dk / 8;                                   // 16-byte pieces per row
 
-  auto load_keys = [&](int page_idx, int buf) {
-    const int pg = __ldcg(bt + page_idx);
+  // a thread's pieces of a key tile: piece i = tid + 256 * n lies in row r(n), column c(n), stepped without dividing
+  const int step_r = LA_THREADS / vecs, step_c = LA_THREADS % vecs;
+  const int first_r = tid / vecs, first_c = tid % vecs;
+  auto load_keys = [&](int pg, int buf) {
     __nv_bfloat16* dst = Ks + (size_t)buf * LA_KEYS * ldk;
-    for (int i = tid; i < LA_KEYS * vecs; i += LA_THREADS) {
-      const int r = i / vecs, c = (i - r * vecs) * 8;
-      if (pg >= 0) la_cp_async16(dst + (size_t)r * ldk + c, pool + ((int64_t)pg * LA_KEYS + r) * dk + c);
-      else *reinterpret_cast<uint4*>(dst + (size_t)r * ldk + c) = make_uint4(0, 0, 0, 0);
+    int r = first_r, c = first_c;
+    while (r < LA_KEYS) {
+      if (pg >= 0) la_cp_async16(dst + (size_t)r * ldk + c * 8, pool + ((int64_t)pg * LA_KEYS + r) * dk + c * 8);
+      else *reinterpret_cast<uint4*>(dst + (size_t)r * ldk + c * 8) = make_uint4(0, 0, 0, 0);
+      r += step_r;
+      c += step_c;
+      if (c >= vecs) { c -= vecs; ++r; }
     }
   };
-
-  if (page_lo <= page_hi) load_keys(page_lo, 0);
+  // page numbers are fetched one step before the copy that needs them, so that no copy waits for its address
+  int pg_next = page_lo <= page_hi ? __ldcg(bt + page_lo) : -1;
+  if (page_lo <= page_hi) load_keys(pg_next, 0);
   la_cp_commit();
+  pg_next = page_lo + 1 <= page_hi ? __ldcg(bt + page_lo + 1) : -1;
   // the queries of the tile; rows beyond the sequence's are zero
   for (int i = tid; i < M * vecs; i += LA_THREADS) {
     const int r = i / vecs, c = (i - r * vecs) * 8;
@@ -140,8 +147,9 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
     const int buf = (pi - page_lo) & 1;
     la_cp_wait_all();
     __syncthreads();                                         // this page's keys (and, the first time, Q) are in place
-    if (pi + 1 <= page_hi) load_keys(pi + 1, buf ^ 1);       // that buffer's last readers passed the barrier above
+    if (pi + 1 <= page_hi) load_keys(pg_next, buf ^ 1);      // that buffer's last readers passed the barrier above
     la_cp_commit();
+    pg_next = pi + 2 <= page_hi ? __ldcg(bt + pi + 2) : -1;
     const __nv_bfloat16* Kt = Ks + (size_t)buf * LA_KEYS * ldk;
 
     // scores of all rows against this warp's 8 keys
@@ -152,21 +160,35 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int u = 0; u < KS; ++u) { sk[mt][u][0] = sk[mt][u][1] = sk[mt][u][2] = sk[mt][u][3] = 0.0f; }
-    for (int k0 = 0; k0 < dk; k0 += 16 * KS) {
+    // (the instructions below keep their order: a group's fragments are asked for before the group before it is
+    // multiplied, so that loads and products overlap)
+    uint32_t bfr[2][KS][2], afr[2][KS][MT][4];
+    auto load_group = [&](int k0, int which) {
 #pragma unroll
       for (int u = 0; u < KS; ++u) {
         const int kk = k0 + 16 * u;
         if (kk < dk) {
-          uint32_t bf[2];
-          la_ldmatrix_x2(bf, Kt + (size_t)bk_row * ldk + kk + bk_col);
+          la_ldmatrix_x2(bfr[which][u], Kt + (size_t)bk_row * ldk + kk + bk_col);
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            uint32_t af[4];
-            la_ldmatrix_x4(af, Qs + (size_t)(mt * 16 + a_row) * ldk + kk + a_col);
-            la_mma(sk[mt][u], af, bf[0], bf[1]);
-          }
+          for (int mt = 0; mt < MT; ++mt) la_ldmatrix_x4(afr[which][u][mt], Qs + (size_t)(mt * 16 + a_row) * ldk + kk + a_col);
         }
       }
+    };
+    auto mul_group = [&](int k0, int which) {
+#pragma unroll
+      for (int u = 0; u < KS; ++u) {
+        if (k0 + 16 * u < dk) {
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) la_mma(sk[mt][u], afr[which][u][mt], bfr[which][u][0], bfr[which][u][1]);
+        }
+      }
+    };
+    load_group(0, 0);
+    for (int k0 = 0; k0 < dk; k0 += 32 * KS) {
+      if (k0 + 16 * KS < dk) load_group(k0 + 16 * KS, 1);
+      mul_group(k0, 0);
+      if (k0 + 32 * KS < dk) load_group(k0 + 32 * KS, 0);
+      if (k0 + 16 * KS < dk) mul_group(k0 + 16 * KS, 1);
     }
     float s[MT][4];
 #pragma unroll
@@ -243,19 +265,22 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
     }
 #pragma unroll
     for (int kk = 0; kk < LA_KEYS; kk += 16) {
-      uint32_t pf[MT][4];
+      uint32_t pf[MT][4], vf[LA_MAX_PAIRS][4];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) la_ldmatrix_x4(pf[mt], Ps + (size_t)(mt * 16 + a_row) * ldp + kk + a_col);
 #pragma unroll
       for (int i = 0; i < LA_MAX_PAIRS; ++i) {
         const int col = (warp + LA_WARPS * i) * 16;
+        if (col < dv) la_ldmatrix_x4_trans(vf[i], Kt + (size_t)(kk + bv_row) * ldk + col + bv_col);
+      }
+#pragma unroll
+      for (int i = 0; i < LA_MAX_PAIRS; ++i) {
+        const int col = (warp + LA_WARPS * i) * 16;
         if (col < dv) {
-          uint32_t vf[4];
-          la_ldmatrix_x4_trans(vf, Kt + (size_t)(kk + bv_row) * ldk + col + bv_col);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            la_mma(o[mt][i][0], pf[mt], vf[0], vf[1]);
-            la_mma(o[mt][i][1], pf[mt], vf[2], vf[3]);
+            la_mma(o[mt][i][0], pf[mt], vf[i][0], vf[i][1]);
+            la_mma(o[mt][i][1], pf[mt], vf[i][2], vf[i][3]);
           }
         }
       }

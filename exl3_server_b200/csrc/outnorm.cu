@@ -140,6 +140,18 @@ __global__ void xielu_kernel(const void* z, int z_dtype, const void* __restrict_
   }
 }
 
+// exp(v) - 1 - v for v <= 0.  Near zero the two subtractions would cancel: there the series v^2/2 + v^3/6 + ... (to
+// v^7, below 1e-8 of the result for |v| < 1/4); elsewhere the plain expression.
+template <bool FAST>
+__device__ inline float xielu_neg(float v) {
+  if (!FAST) return expm1f(v) - v;
+  if (v > -0.25f) {
+    const float p = fmaf(v, fmaf(v, fmaf(v, fmaf(v, fmaf(v, 1.0f / 5040.0f, 1.0f / 720.0f), 1.0f / 120.0f), 1.0f / 24.0f), 1.0f / 6.0f), 0.5f);
+    return v * v * p;
+  }
+  return __expf(v) - 1.0f - v;
+}
+
 template <typename TI, typename TO>
 __global__ void xielu_vec_kernel(const TI* z, const void* __restrict__ pq, int pq_dtype, TO* out, int64_t n8) {
   pdl_wait();
@@ -150,7 +162,9 @@ __global__ void xielu_vec_kernel(const TI* z, const void* __restrict__ pq, int p
     float v[8];
     on_load8(z + i * 8, v, true);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = v[e] > 0.0f ? fmaf(ap * v[e], v[e], 0.5f * v[e]) : fmaf(an, expm1f(v[e]) - v[e], 0.5f * v[e]);
+    // results rounded to 16 bits take the short way to the exponential; float32 results the exact one
+    for (int e = 0; e < 8; ++e)
+      v[e] = v[e] > 0.0f ? fmaf(ap * v[e], v[e], 0.5f * v[e]) : fmaf(an, xielu_neg<sizeof(TO) == 2>(v[e]), 0.5f * v[e]);
     on_store8(out + i * 8, v);
   }
 }
