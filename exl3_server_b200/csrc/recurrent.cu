@@ -64,99 +64,93 @@ mingru_scan_kernel(const void* zug, int zug_dtype, void* y, int y_dtype, float* 
   *sp = S;
 }
 
-constexpr int RC_CHUNK = 64;
+constexpr int RC_CHUNK = 32;
 
 // Chunk j of batch row b has a place of its own among floor(T / RC_CHUNK) + B + 1 places: rows are packed one after
 // another, so floor(first token / RC_CHUNK) + b + j never meets another row's.
 __device__ inline int rc_chunk_place(int t0, int b, int j) { return t0 / RC_CHUNK + b + j; }
 
-// Two neighbouring channels as floats (c even; rows of zug and y start 8-byte aligned when width is even).
-__device__ inline float2 rc_load2(const void* p, int dtype, int64_t i) {
-  if (dtype == DT_F32) return __ldcg(reinterpret_cast<const float2*>(static_cast<const float*>(p) + i));
-  const __nv_bfloat162 v = __ldcg(reinterpret_cast<const __nv_bfloat162*>(static_cast<const __nv_bfloat16*>(p) + i));
-  return __bfloat1622float2(v);
-}
-__device__ inline void rc_step(float a, float u, float& S) {
-  const float z = rc_sigmoid(a);
-  const float cand = u >= 0.0f ? u + 0.5f : rc_sigmoid(u);
-  S = fmaf(z, cand, (1.0f - z) * S);
+// The chunk kernels.  FAST (16-bit projections, whose own rounding is 2^-9): the exponentials and reciprocals of the
+// gates by the short instructions (2^-21 or so); float32 projections take the exact ones.
+template <bool FAST>
+__device__ inline float rc_sig(float v) {
+  return FAST ? __fdividef(1.0f, 1.0f + __expf(-v)) : 1.0f / (1.0f + expf(-v));
 }
 
-// The chunk kernels: a thread owns two neighbouring channels (width even), so a warp reads 128 or 256 bytes a row.
+template <bool FAST>
 __global__ void __launch_bounds__(128)
 mingru_chunk_kernel(const void* zug, int zug_dtype, float* ab, const int* __restrict__ row_start, int width, int places) {
   pdl_wait();
   pdl_trigger();
   const int b = blockIdx.z, j = blockIdx.y;
-  const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int t0 = __ldcg(row_start + b), t1 = __ldcg(row_start + b + 1);
   const int a0 = t0 + j * RC_CHUNK;
   if (c >= width || a0 + RC_CHUNK >= t1) return;       // the row's last chunk has nobody after it
   const int64_t ld = 3 * (int64_t)width;
-  float A0 = 1.0f, A1 = 1.0f, B0 = 0.0f, B1 = 0.0f;
+  float A = 1.0f, Bv = 0.0f;
   for (int t = a0; t < a0 + RC_CHUNK; t += RC_AHEAD) {
-    float2 a[RC_AHEAD], u[RC_AHEAD];
+    float a[RC_AHEAD], u[RC_AHEAD];
 #pragma unroll
     for (int i = 0; i < RC_AHEAD; ++i) {
-      a[i] = rc_load2(zug, zug_dtype, (int64_t)(t + i) * ld + c);
-      u[i] = rc_load2(zug, zug_dtype, (int64_t)(t + i) * ld + c + width);
+      a[i] = rc_load(zug, zug_dtype, (int64_t)(t + i) * ld + c);
+      u[i] = rc_load(zug, zug_dtype, (int64_t)(t + i) * ld + c + width);
     }
 #pragma unroll
     for (int i = 0; i < RC_AHEAD; ++i) {
-      A0 *= 1.0f - rc_sigmoid(a[i].x);
-      A1 *= 1.0f - rc_sigmoid(a[i].y);
-      rc_step(a[i].x, u[i].x, B0);
-      rc_step(a[i].y, u[i].y, B1);
+      const float z = rc_sig<FAST>(a[i]);
+      const float cand = u[i] >= 0.0f ? u[i] + 0.5f : rc_sig<FAST>(u[i]);
+      A *= 1.0f - z;
+      Bv = fmaf(z, cand, (1.0f - z) * Bv);
     }
   }
   const int64_t at = (int64_t)rc_chunk_place(t0, b, j) * width + c;
-  *reinterpret_cast<float2*>(ab + at) = make_float2(A0, A1);
-  *reinterpret_cast<float2*>(ab + (int64_t)places * width + at) = make_float2(B0, B1);
+  ab[at] = A;
+  ab[(int64_t)places * width + at] = Bv;
 }
 
+template <bool FAST>
 __global__ void __launch_bounds__(128)
 mingru_chunk_scan_kernel(const void* zug, int zug_dtype, void* y, int y_dtype, float* state, const float* ab,
                          const int* __restrict__ slot_ids, const int* __restrict__ row_start, int width, int places) {
   pdl_wait();
   pdl_trigger();
   const int b = blockIdx.z, j = blockIdx.y;
-  const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int t0 = __ldcg(row_start + b), t1 = __ldcg(row_start + b + 1);
   const int a0 = t0 + j * RC_CHUNK;
   if (c >= width || a0 >= t1) return;
   float* sp = state + (int64_t)__ldcg(slot_ids + b) * width + c;
-  float2 S = __ldcg(reinterpret_cast<const float2*>(sp));
+  float S = __ldcg(sp);
   for (int i = 0; i < j; ++i) {                        // the chunks before this one, in order
     const int64_t at = (int64_t)rc_chunk_place(t0, b, i) * width + c;
-    const float2 A = __ldcg(reinterpret_cast<const float2*>(ab + at));
-    const float2 Bv = __ldcg(reinterpret_cast<const float2*>(ab + (int64_t)places * width + at));
-    S.x = fmaf(A.x, S.x, Bv.x);
-    S.y = fmaf(A.y, S.y, Bv.y);
+    S = fmaf(__ldcg(ab + at), S, __ldcg(ab + (int64_t)places * width + at));
   }
   const int a1 = min(a0 + RC_CHUNK, t1);
   const int64_t ld = 3 * (int64_t)width;
   for (int t = a0; t < a1; t += RC_AHEAD) {
-    float2 a[RC_AHEAD], u[RC_AHEAD], g[RC_AHEAD];
+    float a[RC_AHEAD], u[RC_AHEAD], g[RC_AHEAD];
 #pragma unroll
     for (int i = 0; i < RC_AHEAD; ++i) {
       const int64_t at = (int64_t)(t + i < a1 ? t + i : t) * ld + c;
-      a[i] = rc_load2(zug, zug_dtype, at);
-      u[i] = rc_load2(zug, zug_dtype, at + width);
-      g[i] = rc_load2(zug, zug_dtype, at + 2 * (int64_t)width);
+      a[i] = rc_load(zug, zug_dtype, at);
+      u[i] = rc_load(zug, zug_dtype, at + width);
+      g[i] = rc_load(zug, zug_dtype, at + 2 * (int64_t)width);
     }
 #pragma unroll
     for (int i = 0; i < RC_AHEAD; ++i) {
       if (t + i < a1) {
-        rc_step(a[i].x, u[i].x, S.x);
-        rc_step(a[i].y, u[i].y, S.y);
-        const float o0 = S.x * g[i].x * rc_sigmoid(g[i].x), o1 = S.y * g[i].y * rc_sigmoid(g[i].y);
+        const float z = rc_sig<FAST>(a[i]);
+        const float cand = u[i] >= 0.0f ? u[i] + 0.5f : rc_sig<FAST>(u[i]);
+        S = fmaf(z, cand, (1.0f - z) * S);
+        const float o = S * g[i] * rc_sig<FAST>(g[i]);
         const int64_t oi = (int64_t)(t + i) * width + c;
-        if (y_dtype == DT_F32) *reinterpret_cast<float2*>(static_cast<float*>(y) + oi) = make_float2(o0, o1);
-        else *reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(y) + oi) = __floats2bfloat162_rn(o0, o1);
+        if (y_dtype == DT_F32) static_cast<float*>(y)[oi] = o;
+        else static_cast<__nv_bfloat16*>(y)[oi] = __float2bfloat16_rn(o);
       }
     }
   }
-  if (a1 == t1) *reinterpret_cast<float2*>(sp) = S;     // the row's last chunk leaves the state
+  if (a1 == t1) *sp = S;                               // the row's last chunk leaves the state
 }
 
 }  // namespace exl3
@@ -164,7 +158,7 @@ mingru_chunk_scan_kernel(const void* zug, int zug_dtype, void* y, int y_dtype, f
 using namespace exl3;
 
 extern "C" size_t exl3_mingru_scratch_bytes(int B, int T, int width, int max_new) {
-  if (max_new <= 2 * RC_CHUNK || width % 2 != 0) return 0;      // few tokens, or an odd width: one thread walks a row's channel
+  if (max_new <= 4 * RC_CHUNK) return 0;                       // few tokens: one thread walks a row's channel
   return 2 * (size_t)(T / RC_CHUNK + B + 1) * width * sizeof(float);
 }
 
@@ -176,19 +170,26 @@ extern "C" int exl3_mingru_scan(const void* zug, int zug_dtype, void* y, int y_d
     set_error("mingru_scan: bad sizes rows=%d tokens=%d width=%d", B, T, width);
     return ERR_BAD_ARGUMENT;
   }
-  if (max_new > 2 * RC_CHUNK && width % 2 == 0) {
+  if (max_new > 4 * RC_CHUNK) {
     // prompts: chunks side by side (see the top of the file)
     const int chunks = ceil_div(max_new, RC_CHUNK), places = T / RC_CHUNK + B + 1;
     if (scratch == nullptr || exl3_mingru_scratch_bytes(B, T, width, max_new) > scratch_bytes || chunks > 65535) {
       set_error("mingru_scan: scratch of %zu bytes is too small for %d tokens", scratch_bytes, T);
       return ERR_SCRATCH;
     }
-    dim3 grid(ceil_div(width / 2, 128), chunks, B);
-    launch_pdl(mingru_chunk_kernel, grid, dim3(128), 0, stream, zug, zug_dtype, scratch, row_start, width, places);
+    dim3 grid(ceil_div(width, 128), chunks, B);
+    if (zug_dtype == DT_BF16)
+      launch_pdl(mingru_chunk_kernel<true>, grid, dim3(128), 0, stream, zug, zug_dtype, scratch, row_start, width, places);
+    else
+      launch_pdl(mingru_chunk_kernel<false>, grid, dim3(128), 0, stream, zug, zug_dtype, scratch, row_start, width, places);
     int rc = launch_status("mingru_chunk");
     if (rc) return rc;
-    launch_pdl(mingru_chunk_scan_kernel, grid, dim3(128), 0, stream, zug, zug_dtype, y, y_dtype, state,
-               (const float*)scratch, slot_ids, row_start, width, places);
+    if (zug_dtype == DT_BF16)
+      launch_pdl(mingru_chunk_scan_kernel<true>, grid, dim3(128), 0, stream, zug, zug_dtype, y, y_dtype, state,
+                 (const float*)scratch, slot_ids, row_start, width, places);
+    else
+      launch_pdl(mingru_chunk_scan_kernel<false>, grid, dim3(128), 0, stream, zug, zug_dtype, y, y_dtype, state,
+                 (const float*)scratch, slot_ids, row_start, width, places);
     return launch_status("mingru_chunk_scan");
   }
   launch_pdl(mingru_scan_kernel, dim3(ceil_div(width, 128), B), dim3(128), 0, stream, zug, zug_dtype, y, y_dtype, state,
