@@ -33,7 +33,7 @@ def parse_ids(text: str) -> List[int]:
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(
         prog="exl3-server-b200", allow_abbrev=False,
-        description="Llama-family generation on one B200: token ids in, token ids out")
+        description="generation on one B200 for the registered architectures: token ids in, token ids out")
     ap.add_argument("--model", required=True, metavar="DIR", help="folder with config.json and model.safetensors")
     ap.add_argument("-p", "--prompt", action="append", type=parse_ids, default=[], metavar="IDS",
                     help="prompt as token ids, e.g. \"1,15,27\" (repeatable; prompts run as a batch)")
