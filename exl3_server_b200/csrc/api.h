@@ -35,6 +35,11 @@ int exl3_gemm_simt(const void* x, const void* w, const void* bias, void* y, int 
 int exl3_gemv_bf16(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N,
                    int K, int epilogue, cudaStream_t stream);
 
+// exl3_gemv_bf16 (epilogue 0) with the xIELU activation on its results: act_p z^2 + z / 2 for z > 0, act_n (exp(z) - 1 - z)
+// + z / 2 otherwise, with act_p = softplus(p) and act_n = 1/2 + softplus(q) given by the caller.
+int exl3_gemv_bf16_act(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N, int K,
+                       float act_p, float act_n, cudaStream_t stream);
+
 // bfloat16 GEMM on tcgen05 tensor cores with TMA loads (K and N multiples of 8); epilogue 1 as in
 // exl3_gemv_bf16 (N a multiple of 16, output N/2 wide).  exl3_gemm_tc_status() returns and clears the
 // code a kernel left when one of its bounded waits ran out (0: none).

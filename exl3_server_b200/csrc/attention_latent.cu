@@ -80,10 +80,10 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
 
   pdl_wait();
   pdl_trigger();
-  const int b = blockIdx.x, sp = blockIdx.z;
+  const int b = blockIdx.y, sp = blockIdx.z;                 // tiles along x: a long prompt of many heads has many
   const int tok0 = __ldcg(row_start + b);
   const int F = (__ldcg(row_start + b + 1) - tok0) * H;      // rows of this sequence in this step
-  const int f0 = blockIdx.y * M;
+  const int f0 = blockIdx.x * M;
   if (f0 >= F) return;
   const int pos0 = __ldcg(row_pos0 + b);
   const int rows = min(M, F - f0);
@@ -387,7 +387,7 @@ static int la_launch(const void* q, void* out, const void* pool, const int* bloc
     set_error("attn_latent: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
     return (int)e;
   }
-  dim3 grid(B, ceil_div(max_rows, 16 * MT), n_splits);
+  dim3 grid(ceil_div(max_rows, 16 * MT), B, n_splits);
   launch_pdl(attn_latent_kernel<MT>, grid, dim3(LA_THREADS), smem, stream, static_cast<const __nv_bfloat16*>(q),
              static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(pool), block_table, bt_stride, row_start,
              row_pos0, H, dk, dv, scale * 1.4426950408889634f, pages_per_chunk, n_splits, scratch, gate);
@@ -431,7 +431,7 @@ extern "C" int exl3_attn_latent(const void* q, void* out, const void* pool, cons
     return ERR_SCRATCH;
   }
   const int64_t max_rows64 = (int64_t)max_new * H;
-  if (max_rows64 > 65535LL * 16 || B > 0x7fffffff) { set_error("attn_latent: grid too large"); return ERR_UNSUPPORTED; }
+  if (max_rows64 > 0x7fffffffLL || B > 65535) { set_error("attn_latent: grid too large"); return ERR_UNSUPPORTED; }
   const int max_rows = (int)max_rows64;
   const int mt = exl3_attn_latent_row_tile(dk, max_rows);
   int rc;

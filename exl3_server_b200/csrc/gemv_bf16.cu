@@ -29,3 +29,27 @@ extern "C" int exl3_gemv_bf16(const void* x, const void* w, const void* bias, vo
 #undef EXL3_GEMV_ST
 #undef EXL3_GEMV
 }
+
+// The plain projection with the xIELU activation on its results (EPI 3 in gemv_bf16.cuh): act_p = softplus(p),
+// act_n = 1/2 + softplus(q).
+extern "C" int exl3_gemv_bf16_act(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M,
+                                  int N, int K, float act_p, float act_n, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (M < 0 || M > 16 || N < 0 || K < 8 || K % 8 != 0) {
+    set_error("gemv_bf16_act: needs 1 <= M <= 16 and K a multiple of 8, got M=%d N=%d K=%d", M, N, K);
+    return ERR_BAD_ARGUMENT;
+  }
+  if (!aligned16(x) || !aligned16(w)) { set_error("gemv_bf16_act: x and w must be 16-byte aligned"); return ERR_ALIGNMENT; }
+  const bool f32 = out_dtype == DT_F32;
+  if (!f32 && out_dtype != DT_BF16) { set_error("gemv_bf16_act: unsupported output type %d", out_dtype); return ERR_UNSUPPORTED; }
+  GemvNorm nrm = {};
+  nrm.act_p = act_p;
+  nrm.act_n = act_n;
+  int warps, stages;
+  const int nt = gemv_shape(M, N, K, warps, stages);
+  if (nt == 1)
+    return f32 ? launch<1, float, 3, gemv_stages(1)>(x, w, bias, y, M, N, K, warps, stream, nrm)
+               : launch<1, __nv_bfloat16, 3, gemv_stages(1)>(x, w, bias, y, M, N, K, warps, stream, nrm);
+  return f32 ? launch<2, float, 3, gemv_stages(2)>(x, w, bias, y, M, N, K, warps, stream, nrm)
+             : launch<2, __nv_bfloat16, 3, gemv_stages(2)>(x, w, bias, y, M, N, K, warps, stream, nrm);
+}

@@ -72,9 +72,13 @@ struct GemvNorm {
   const float* ss_in;            // [16, ss_blocks] from the producer
   int ss_blocks;
   float eps, width;
+  // EPI 3: the two constants of the activation applied to the results (see below)
+  float act_p, act_n;
 };
 
-// EPI 0: y[m, n] = acc (+ bias).  EPI 1 (gated feed-forward): the 16 rows of a
+// EPI 0: y[m, n] = acc (+ bias).  EPI 3: the same through the xIELU activation, a(z) = act_p z^2 + z / 2 for z > 0 and
+// act_n (exp(z) - 1 - z) + z / 2 otherwise (act_p = softplus(p), act_n = 1/2 + softplus(q), worked out by the caller).
+// EPI 1 (gated feed-forward): the 16 rows of a
 // block are 8 gate rows followed by the 8 up rows of the same features;
 // y[m, block * 8 + r] = silu(gate_r) * up_r, so N / 2 features come out.
 template <int NT, typename TO, int EPI, int GEMV_STAGES, bool SCALE = false>
@@ -210,7 +214,7 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
     }
   }
   __syncthreads();
-  if (EPI == 0) {
+  if (EPI == 0 || EPI == 3) {
     for (int idx = threadIdx.x; idx < 16 * 8 * NT; idx += blockDim.x) {
       const int m = idx >> 4, r = idx & 15;           // consecutive threads: consecutive features
       const int n = r0 + r;
@@ -219,6 +223,7 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
       for (int wi = 0; wi < nwarps; ++wi) s += part[wi][r][m];
       if (SCALE) s *= s_inv[m];
       if (bias) s += __bfloat162float(bias[n]);
+      if (EPI == 3) s = s > 0.0f ? fmaf(nrm.act_p * s, s, 0.5f * s) : fmaf(nrm.act_n, expm1f(s) - s, 0.5f * s);
       Elem<TO>::store(y + (int64_t)m * N + n, s);
     }
   } else if (EPI == 1) {

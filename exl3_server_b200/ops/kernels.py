@@ -204,6 +204,23 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     return out
 
 
+def gemv_bf16_act(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+                  act_p: float, act_n: float) -> torch.Tensor:
+    """``xielu(x @ w.T (+ bias))`` for at most 16 rows of x, the activation in the projection's own epilogue:
+    ``act_p z^2 + z / 2`` for ``z > 0``, ``act_n (exp(z) - 1 - z) + z / 2`` otherwise."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelLibraryError(f"gemv_bf16_act: x {tuple(x.shape)} and w {tuple(w.shape)} must be bfloat16 and fit")
+    _contig(x, "x")
+    _contig(w, "w")
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _check(library().exl3_gemv_bf16_act(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(dtype_code(out.dtype)),
+                                        _c_int(M), _c_int(N), _c_int(K), _c_float(act_p), _c_float(act_n),
+                                        _stream()), "gemv_bf16_act")
+    return out
+
+
 def gemv_bf16_normed(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
                      gated: bool = False, scale=None, resid=None):
     """``gemv_bf16`` as one or both sides of a norm that is no kernel of its own (see gemv_bf16.cuh).

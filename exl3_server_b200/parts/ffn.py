@@ -9,10 +9,12 @@ inside its kernel.
 ``params["activation"]``.  ``xielu`` has two learned numbers ``p, q`` (tensor
 ``act``): ``softplus(p) z^2 + z/2`` for ``z > 0`` and
 ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z/2`` otherwise; it is computed in
-float32 (from float32 results of the up projection where the projection's kernel has them).
+float32 (from float32 results of the up projection where the projection's kernel has them); for steps of few
+tokens it is the epilogue of the up projection's weight-streaming kernel.
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, List
 
 import torch
@@ -76,8 +78,22 @@ def _xielu(z: torch.Tensor, tensors, out_dtype):
     return K.xielu(z, tensors["act"], out_dtype)
 
 
-# name -> (parameter tensors as (suffix, shape), function(z, {suffix: tensor}, out_dtype))
-ACTIVATIONS = {"xielu": ((("act", (2,)),), _xielu)}
+def _xielu_prepare(tensors) -> None:
+    """softplus(p) and 1/2 + softplus(q), worked out once (float64) from the two stored numbers, when the model is built."""
+    p, q = (float(v) for v in tensors["act"].detach().double().cpu())
+    sp = lambda v: v if v > 30.0 else math.log1p(math.exp(v))
+    tensors["act.constants"] = (sp(p), 0.5 + sp(q))
+
+
+def _xielu_fused(linear: Linear, x: torch.Tensor, tensors, out_dtype):
+    """The up projection with the activation in its epilogue, or None where its kernel has none."""
+    return linear.xielu(x, *tensors["act.constants"], out_dtype)
+
+
+# name -> (parameter tensors as (suffix, shape), function(z, {suffix: tensor}, out_dtype),
+#          function(linear, x, {suffix: tensor}, out_dtype) -> activated projection or None,
+#          function({suffix: tensor}) called once when the part is built)
+ACTIVATIONS = {"xielu": ((("act", (2,)),), _xielu, _xielu_fused, _xielu_prepare)}
 
 
 class DenseFeedForward:
@@ -91,7 +107,7 @@ class DenseFeedForward:
 
     @classmethod
     def tensor_specs(cls, spec: FeedForwardSpec, prefix: str) -> List[TensorSpec]:
-        extra, _ = cls._activation(spec)
+        extra = cls._activation(spec)[0]
         return [TensorSpec(prefix + "up", (spec.inner, spec.width)),
                 TensorSpec(prefix + "down", (spec.width, spec.inner))] + \
                [TensorSpec(prefix + name, shape) for name, shape in extra]
@@ -99,14 +115,18 @@ class DenseFeedForward:
     def __init__(self, spec: FeedForwardSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
         self.spec = spec
         self.dtype = ctx.dtype
-        extra, self.act = self._activation(spec)
+        extra, self.act, self.act_fused, prepare = self._activation(spec)
         self.act_tensors = {name: tensors[prefix + name].contiguous() for name, _ in extra}
+        prepare(self.act_tensors)
         self.up = Linear(tensors[prefix + "up"], None, ctx.dtype)
         self.down = Linear(tensors[prefix + "down"], None, ctx.dtype)
 
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
-        z = self.up(x, out_dtype=self.up.wide_dtype(x.shape[0]))
-        return self.down(self.act(z, self.act_tensors, self.dtype), out_dtype=self.down.wide_dtype(x.shape[0]))
+        a = self.act_fused(self.up, x, self.act_tensors, self.dtype) if self.dtype == torch.bfloat16 else None
+        if a is None:
+            z = self.up(x, out_dtype=self.up.wide_dtype(x.shape[0]))
+            a = self.act(z, self.act_tensors, self.dtype)
+        return self.down(a, out_dtype=self.down.wide_dtype(x.shape[0]))
 
     def weight_bytes(self) -> int:
         return self.up.weight_bytes() + self.down.weight_bytes()

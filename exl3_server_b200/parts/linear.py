@@ -139,6 +139,14 @@ class Linear:
             return torch.float32
         return self.dtype
 
+    def xielu(self, x: torch.Tensor, act_p: float, act_n: float, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+        """The projection with the xIELU activation (constants ``softplus(p)`` and ``1/2 + softplus(q)``) in its own
+        epilogue, where the kernel that takes these rows has it (the weight-streaming GEMV); else None, and the
+        caller projects and activates in two steps."""
+        if isinstance(x, RawNormed) or self._streaming_kernel(x.shape[0]) is not K.gemv_bf16_normed:
+            return None
+        return K.gemv_bf16_act(x, self.weight, self.bias, out_dtype, act_p, act_n)
+
     def streams_weights(self, rows: int) -> bool:
         """Whether ``rows`` rows of input go through a kernel that reads the weights once."""
         return self._streaming_kernel(rows) is not None

@@ -44,6 +44,12 @@ CONFIGS = {
         RigitarLayer("latent_attention", latent(2, 32, 64, 16, 32, 512, 0.12), dense(96)),
         RigitarLayer("latent_attention", latent(5, 8, 0, 8, 16, 272, 0.3, dims=0), None),
     ]),
+    # sizes that are multiples of nothing: no vector access, no tensor-core projection fits
+    "odd": RigitarConfig(vocab=77, width=100, norm_eps=2e-6, layers=[
+        RigitarLayer("latent_attention", latent(3, 10, 6, 12, 20, 36, 0.3, base=300.0), dense(70)),
+        RigitarLayer("mingru", {"width": 50}, dense(30)),
+        RigitarLayer("latent_attention", latent(2, 14, 6, 9, 12, 36, 0.2, base=300.0, kv_from=0), None),
+    ]),
     # one mechanism alone
     "only_latent": RigitarConfig(vocab=128, width=80, norm_eps=1e-6, layers=[
         RigitarLayer("latent_attention", latent(4, 32, 16, 24, 48, 80, 0.18), None)]),

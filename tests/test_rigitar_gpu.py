@@ -18,7 +18,7 @@ from rigitar_configs import CONFIGS, make_rigitar
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"mixed": [1, 2, 9, 64, 65, 150], "heads8": [3, 17, 63, 128, 129, 200], "wide": [1, 5, 40, 66, 70, 130],
+LENGTHS = {"mixed": [1, 2, 9, 64, 65, 150], "odd": [1, 3, 20, 64, 66, 131], "heads8": [3, 17, 63, 128, 129, 200], "wide": [1, 5, 40, 66, 70, 130],
            "only_latent": [1, 2, 31, 64, 129, 140], "only_mingru": [1, 2, 31, 64, 129, 140],
            "only_ff": [1, 2, 31, 64, 129, 140]}
 
