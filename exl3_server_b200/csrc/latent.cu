@@ -91,10 +91,15 @@ latent_prep_kernel(const void* a, int a_dtype, int lda, int q_off, int q_rank, c
   }
 }
 
+// A value that an earlier kernel of the step wrote: through L2 (see load_vec_cg in common.cuh).
+__device__ inline float lt_act(const float* p) { return __ldcg(p); }
+__device__ inline float lt_act(const __nv_bfloat16* p) { return __bfloat162float(__ldcg(p)); }
+
 constexpr int HG_TM = 8;          // tokens per block
 constexpr int HG_TN = 32;         // outputs per block: a warp's lanes
 constexpr int HG_KG = 8;          // warps of a block; each takes every eighth slice of a staged piece of K
-constexpr int HG_KC = 256;        // features of x staged at a time
+constexpr int HG_KC = 512;        // features of x staged at a time
+constexpr int HG_PER = HG_KC / HG_KG;   // features of a staged piece per warp: that many loads of w in flight a thread
 
 // A block takes 8 tokens x 32 outputs of one head.  Its eight warps split the features k between them (a warp's
 // lanes read 32 consecutive outputs of one row of w: one 64- or 128-byte piece), so a token's step, which has one
@@ -108,10 +113,10 @@ head_gemm_kernel(const T* x, int64_t x_row, int x_head, const T* __restrict__ w,
                  const int* __restrict__ tok_pos, int tail_off, int n_blocks) {
   __shared__ float xs[HG_TM][HG_KC];
   __shared__ float part[HG_KG][HG_TM][HG_TN];
-  pdl_wait();
   pdl_trigger();
   const int h = blockIdx.z, t0 = blockIdx.y * HG_TM;
   if ((int)blockIdx.x >= n_blocks) {
+    pdl_wait();
     // the tail of each head's output row: zeros, the rotated features, zeros
     const int half = rot / 2;
     const int span = out_head - N;
@@ -126,10 +131,10 @@ head_gemm_kernel(const T* x, int64_t x_row, int x_head, const T* __restrict__ w,
           const int f = r < half ? r : r - half;
           float sn, cs;
           rope_sincos((float)__ldcg(tok_pos + t), inv_freq[f], inv_freq_lo ? inv_freq_lo[f] : 0.0f, &sn, &cs);
-          const float lo = Elem<T>::load(src + f), hi = Elem<T>::load(src + f + half);
+          const float lo = lt_act(src + f), hi = lt_act(src + f + half);
           v = r < half ? lo * cs - hi * sn : hi * cs + lo * sn;
         } else {
-          v = Elem<T>::load(src + r);
+          v = lt_act(src + r);
         }
       }
       Elem<T>::store(out + (int64_t)t * out_row + (int64_t)h * out_head + i, v);
@@ -143,29 +148,29 @@ head_gemm_kernel(const T* x, int64_t x_row, int x_head, const T* __restrict__ w,
   for (int m = 0; m < HG_TM; ++m) acc[m] = 0.0f;
   const T* wh = w + (int64_t)h * K * N;
   for (int k0 = 0; k0 < K; k0 += HG_KC) {
+    const int kc = min(HG_KC, K - k0);
+    // this warp's features of the piece are kg, kg + 8, ...: all their weights are asked for at once (they depend on
+    // no kernel of the step, so the first piece's are on their way before the wait for the kernel before this one)
+    float wv[HG_PER];
+#pragma unroll
+    for (int u = 0; u < HG_PER; ++u) {
+      const int k = kg + u * HG_KG;
+      wv[u] = (n < N && k < kc) ? Elem<T>::load(wh + (int64_t)(k0 + k) * N + n) : 0.0f;
+    }
+    if (k0 == 0) pdl_wait();
     __syncthreads();
     for (int idx = threadIdx.x; idx < HG_TM * HG_KC; idx += blockDim.x) {
       const int m = idx / HG_KC, k = idx - m * HG_KC, t = t0 + m;
-      xs[m][k] = (t < Tn && k0 + k < K) ? Elem<T>::load(x + (int64_t)t * x_row + (int64_t)h * x_head + k0 + k) : 0.0f;
+      xs[m][k] = (t < Tn && k < kc) ? lt_act(x + (int64_t)t * x_row + (int64_t)h * x_head + k0 + k) : 0.0f;
     }
     __syncthreads();
-    if (n < N) {
-      const int kc = min(HG_KC, K - k0);
-      // this warp's features of the piece: kg, kg + 8, ...  (four loads in flight)
-      int k = kg;
-      for (; k + 3 * HG_KG < kc; k += 4 * HG_KG) {
-        float wv[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) wv[u] = Elem<T>::load(wh + (int64_t)(k0 + k + u * HG_KG) * N + n);
+    for (int u0 = 0; u0 < HG_PER; u0 += 16) {
+      if (u0 * HG_KG < kc) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = u0; u < u0 + 16; ++u)
 #pragma unroll
-          for (int m = 0; m < HG_TM; ++m) acc[m] = fmaf(xs[m][k + u * HG_KG], wv[u], acc[m]);
-      }
-      for (; k < kc; k += HG_KG) {
-        const float wv = Elem<T>::load(wh + (int64_t)(k0 + k) * N + n);
-#pragma unroll
-        for (int m = 0; m < HG_TM; ++m) acc[m] = fmaf(xs[m][k], wv, acc[m]);
+          for (int m = 0; m < HG_TM; ++m) acc[m] = fmaf(xs[m][kg + u * HG_KG], wv[u], acc[m]);
       }
     }
   }
