@@ -98,19 +98,21 @@ __device__ inline float lt_act(const __nv_bfloat16* p) { return __bfloat162float
 constexpr int HG_TM = 8;          // tokens per block
 constexpr int HG_TN = 32;         // outputs per block: a warp's lanes
 constexpr int HG_KG = 8;          // warps of a block; each takes every eighth slice of a staged piece of K
-constexpr int HG_KC = 512;        // features of x staged at a time
-constexpr int HG_PER = HG_KC / HG_KG;   // features of a staged piece per warp: that many loads of w in flight a thread
+// HG_KC, features of x staged at a time, is a parameter of the kernel: 512 for a single block of tokens (HG_KC / 8 = 64
+// loads of w in flight a thread, 128 registers: two blocks an SM, which is plenty for the (N / 32) * heads blocks of a
+// token's step), 128 for many tokens (16 loads, small blocks, eight of them an SM).
 
 // A block takes 8 tokens x 32 outputs of one head.  Its eight warps split the features k between them (a warp's
 // lanes read 32 consecutive outputs of one row of w: one 64- or 128-byte piece), so a token's step, which has one
 // block of tokens, still has (N / 32) * heads blocks of 256 threads with K / 8 loads each in flight, and the
 // partial sums meet in shared memory in the order of the warps.
-template <typename T>
+template <typename T, int HG_KC>
 __global__ void __launch_bounds__(HG_TN * HG_KG)
 head_gemm_kernel(const T* x, int64_t x_row, int x_head, const T* __restrict__ w, T* out, int64_t out_row, int out_head,
                  int Tn, int heads, int K, int N, const float* mul, int rot_dim, int rot,
                  const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo,
                  const int* __restrict__ tok_pos, int tail_off, int n_blocks) {
+  constexpr int HG_PER = HG_KC / HG_KG;
   __shared__ float xs[HG_TM][HG_KC];
   __shared__ float part[HG_KG][HG_TM][HG_TN];
   pdl_trigger();
@@ -244,17 +246,19 @@ extern "C" int exl3_head_gemm(const void* x, int64_t x_row, int x_head, const vo
     return 0;
   }
   dim3 grid(n_blocks + tail, rows, heads);
+#define EXL3_HG(TT, KC)                                                                                              \
+  launch_pdl(head_gemm_kernel<TT, KC>, grid, dim3(HG_TN * HG_KG), 0, stream, static_cast<const TT*>(x), x_row, x_head,  \
+             static_cast<const TT*>(w), static_cast<TT*>(out), out_row, out_head, T, heads, K, N, mul, rot_dim, rot,    \
+             inv_freq, inv_freq_lo, tok_pos, tail_off, n_blocks)
+  const bool few = rows == 1 && K > 128;
   if (dtype == DT_F32) {
-    launch_pdl(head_gemm_kernel<float>, grid, dim3(HG_TN * HG_KG), 0, stream, static_cast<const float*>(x), x_row, x_head,
-               static_cast<const float*>(w), static_cast<float*>(out), out_row, out_head, T, heads, K, N, mul, rot_dim, rot,
-               inv_freq, inv_freq_lo, tok_pos, tail_off, n_blocks);
+    if (few) EXL3_HG(float, 512); else EXL3_HG(float, 128);
   } else if (dtype == DT_BF16) {
-    launch_pdl(head_gemm_kernel<__nv_bfloat16>, grid, dim3(HG_TN * HG_KG), 0, stream, static_cast<const __nv_bfloat16*>(x), x_row,
-               x_head, static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(out), out_row, out_head, T, heads,
-               K, N, mul, rot_dim, rot, inv_freq, inv_freq_lo, tok_pos, tail_off, n_blocks);
+    if (few) EXL3_HG(__nv_bfloat16, 512); else EXL3_HG(__nv_bfloat16, 128);
   } else {
     set_error("head_gemm: unsupported element type %d", dtype);
     return ERR_UNSUPPORTED;
   }
+#undef EXL3_HG
   return launch_status("head_gemm");
 }
