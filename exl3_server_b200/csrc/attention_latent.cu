@@ -154,7 +154,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
 
     // scores of all rows against this warp's 8 keys
     // (with few row tiles the features go round KS sums per tile, so that the chain of dependent products is short)
-    constexpr int KS = MT >= 4 ? 1 : 4 / MT;
+    constexpr int KS = MT >= 3 ? 1 : 4 / MT;
     float sk[MT][KS][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -399,10 +399,10 @@ static int la_launch(const void* q, void* out, const void* pool, const int* bloc
 using namespace exl3;
 
 extern "C" int exl3_attn_latent_row_tile(int dk, int max_rows) {
-  // the largest tile of rows (in sixteens: 4, 2 or 1) that a sequence's rows fill and whose shared memory fits; 0: none
+  // the largest tile of rows (in sixteens: 4, 3, 2 or 1) that a sequence's rows fill and whose shared memory fits; 0: none
   const size_t limit = 227 * 1024;
-  int mt = max_rows > 32 ? 4 : (max_rows > 16 ? 2 : 1);
-  while (mt >= 1 && la_smem_bytes(mt, dk) > limit) mt >>= 1;
+  int mt = max_rows > 48 ? 4 : (max_rows > 32 ? 3 : (max_rows > 16 ? 2 : 1));
+  while (mt >= 1 && la_smem_bytes(mt, dk) > limit) --mt;
   return mt;
 }
 
@@ -435,7 +435,8 @@ extern "C" int exl3_attn_latent(const void* q, void* out, const void* pool, cons
   const int max_rows = (int)max_rows64;
   const int mt = exl3_attn_latent_row_tile(dk, max_rows);
   int rc;
-  if (mt == 4) rc = la_launch<4>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
+  if (mt == 3) rc = la_launch<3>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
+  else if (mt == 4) rc = la_launch<4>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
   else if (mt == 2) rc = la_launch<2>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
   else if (mt == 1) rc = la_launch<1>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
   else { set_error("attn_latent: rows of %d features do not fit shared memory", dk); return ERR_UNSUPPORTED; }
