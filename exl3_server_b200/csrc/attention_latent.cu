@@ -20,6 +20,7 @@
 #include "common.cuh"
 
 #include <math.h>
+#include <stdlib.h>
 
 namespace exl3 {
 
@@ -27,6 +28,7 @@ constexpr int LA_WARPS = 8;
 constexpr int LA_THREADS = LA_WARPS * 32;
 constexpr int LA_KEYS = 64;                // keys per step: one page
 constexpr int LA_PAD = 8;                  // elements added to a shared-memory row: 16-byte pieces of consecutive rows fall into different banks
+constexpr int LA_COPY_WARPS = 4;           // warps that only copy pages, in the kernel's form that has them
 constexpr int LA_MAX_PAIRS = 4;            // 16-column slices of the values per warp: dv <= 8 * 4 * 16 = 512
 
 __device__ inline void la_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
@@ -54,14 +56,18 @@ __device__ inline void la_cp_async16(void* dst, const void* src) {
 }
 __device__ inline void la_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ inline void la_cp_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ inline void la_bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ inline void la_bar_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 __device__ inline float la_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
-template <int MT>
-__global__ void __launch_bounds__(LA_THREADS, 1)
+// PW: four more warps do nothing but copy the pages (see the top of the file); the eight others then meet at named
+// barriers: 1 among themselves, 2 + buffer when a page has landed, 4 + buffer when they are done with it.
+template <int MT, bool PW>
+__global__ void __launch_bounds__(LA_THREADS + (PW ? 32 * LA_COPY_WARPS : 0), 1)
 attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat16* pool, const int* __restrict__ block_table,
                    int bt_stride, const int* __restrict__ row_start, const int* __restrict__ row_pos0, int H, int dk, int dv,
                    float scale_log2, int pages_per_chunk, int n_splits, float* scratch, const float* gate) {
@@ -97,9 +103,15 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
   const int* bt = block_table + (int64_t)b * bt_stride;
   const int vecs = dk / 8;                                   // 16-byte pieces per row
 
-  // a thread's pieces of a key tile: piece i = tid + 256 * n lies in row r(n), column c(n), stepped without dividing
-  const int step_r = LA_THREADS / vecs, step_c = LA_THREADS % vecs;
-  const int first_r = tid / vecs, first_c = tid % vecs;
+  constexpr int ALL = LA_THREADS + 32 * LA_COPY_WARPS;              // the threads that meet at the barriers between the copying warp and the others
+  auto sync_compute = [&]() {
+    if constexpr (PW) la_bar_sync(1, LA_THREADS); else __syncthreads();
+  };
+  // a thread's pieces of a key tile: piece i = index + copiers * n lies in row r(n), column c(n), stepped without dividing
+  constexpr int COPIERS = PW ? 32 * LA_COPY_WARPS : LA_THREADS;
+  const int ci = PW ? tid - LA_THREADS : tid;         // (meaningful in the copying warps only when there are such)
+  const int step_r = COPIERS / vecs, step_c = COPIERS % vecs;
+  const int first_r = ci / vecs, first_c = ci % vecs;
   auto load_keys = [&](int pg, int buf) {
     __nv_bfloat16* dst = Ks + (size_t)buf * LA_KEYS * ldk;
     int r = first_r, c = first_c;
@@ -113,9 +125,27 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
   };
   // page numbers are fetched one step before the copy that needs them, so that no copy waits for its address
   int pg_next = page_lo <= page_hi ? __ldcg(bt + page_lo) : -1;
-  if (page_lo <= page_hi) load_keys(pg_next, 0);
-  la_cp_commit();
-  pg_next = page_lo + 1 <= page_hi ? __ldcg(bt + page_lo + 1) : -1;
+  if constexpr (PW) {
+    if (warp >= LA_WARPS) {
+      // the copying warp: a page into the buffer that the others have let go of, then the word that it has landed
+      for (int pi = page_lo; pi <= page_hi; ++pi) {
+        const int buf = (pi - page_lo) & 1;
+        const int pg = pg_next;
+        pg_next = pi + 1 <= page_hi ? __ldcg(bt + pi + 1) : -1;
+        if (pi - page_lo >= 2) la_bar_sync(4 + buf, ALL);
+        load_keys(pg, buf);
+        la_cp_commit();
+        la_cp_wait_all();
+        __threadfence_block();
+        la_bar_arrive(2 + buf, ALL);
+      }
+      return;
+    }
+  } else {
+    if (page_lo <= page_hi) load_keys(pg_next, 0);
+    la_cp_commit();
+    pg_next = page_lo + 1 <= page_hi ? __ldcg(bt + page_lo + 1) : -1;
+  }
   // the queries of the tile; rows beyond the sequence's are zero
   for (int i = tid; i < M * vecs; i += LA_THREADS) {
     const int r = i / vecs, c = (i - r * vecs) * 8;
@@ -124,6 +154,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
     *reinterpret_cast<uint4*>(Qs + (size_t)r * ldk + c) = v;
   }
   if (tid < M) { m_run[tid] = -INFINITY; l_run[tid] = 0.0f; }
+  if constexpr (PW) sync_compute();                          // (without a copying warp the loop's first barrier does this)
 
   float o[MT][LA_MAX_PAIRS][2][4];
 #pragma unroll
@@ -145,11 +176,15 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
 
   for (int pi = page_lo; pi <= page_hi; ++pi) {
     const int buf = (pi - page_lo) & 1;
-    la_cp_wait_all();
-    __syncthreads();                                         // this page's keys (and, the first time, Q) are in place
-    if (pi + 1 <= page_hi) load_keys(pg_next, buf ^ 1);      // that buffer's last readers passed the barrier above
-    la_cp_commit();
-    pg_next = pi + 2 <= page_hi ? __ldcg(bt + pi + 2) : -1;
+    if constexpr (PW) {
+      la_bar_sync(2 + buf, ALL);                             // this page's keys have landed
+    } else {
+      la_cp_wait_all();
+      __syncthreads();                                       // this page's keys (and, the first time, Q) are in place
+      if (pi + 1 <= page_hi) load_keys(pg_next, buf ^ 1);    // that buffer's last readers passed the barrier above
+      la_cp_commit();
+      pg_next = pi + 2 <= page_hi ? __ldcg(bt + pi + 2) : -1;
+    }
     const __nv_bfloat16* Kt = Ks + (size_t)buf * LA_KEYS * ldk;
 
     // scores of all rows against this warp's 8 keys
@@ -217,7 +252,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
         if ((lane & 3) == 0) red_max[warp * M + r] = mx;
       }
     }
-    __syncthreads();
+    sync_compute();
     if (tid < M) {
       float mx = red_max[tid];
 #pragma unroll
@@ -226,7 +261,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
       corr[tid] = mn == -INFINITY ? 1.0f : la_exp2(mo - mn);      // exp2(-inf) = 0 the first time
       m_run[tid] = mn;
     }
-    __syncthreads();
+    sync_compute();
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -244,7 +279,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
         if ((lane & 3) == 0) red_sum[warp * M + r] = sm;
       }
     }
-    __syncthreads();
+    sync_compute();
     if (tid < M) {
       float sm = 0.0f;
 #pragma unroll
@@ -285,10 +320,13 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
         }
       }
     }
-    __syncthreads();                                         // P, the statistics and this key tile are free again
+    if constexpr (PW) {
+      if (pi + 2 <= page_hi) la_bar_arrive(4 + buf, ALL);    // the copying warp may fill this buffer again
+    }
+    sync_compute();                                          // P, the statistics and (without a copying warp) this key tile are free again
   }
   la_cp_wait_all();
-  __syncthreads();                                           // the statistics, also when the chunk held no page
+  sync_compute();                                            // the statistics, also when the chunk held no page
 
   // results: rows qr and qr + 8 of every row tile, this warp's column slices
 #pragma unroll
@@ -377,18 +415,18 @@ static size_t la_smem_bytes(int MT, int dk) {
          (2 * LA_WARPS * M + 3 * M) * sizeof(float);
 }
 
-template <int MT>
+template <int MT, bool PW>
 static int la_launch(const void* q, void* out, const void* pool, const int* block_table, int bt_stride, const int* row_start,
                      const int* row_pos0, int B, int max_rows, int H, int dk, int dv, float scale, int pages_per_chunk,
                      int n_splits, float* scratch, const float* gate, cudaStream_t stream) {
   const size_t smem = la_smem_bytes(MT, dk);
-  cudaError_t e = cudaFuncSetAttribute(attn_latent_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(attn_latent_kernel<MT, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("attn_latent: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
     return (int)e;
   }
   dim3 grid(ceil_div(max_rows, 16 * MT), B, n_splits);
-  launch_pdl(attn_latent_kernel<MT>, grid, dim3(LA_THREADS), smem, stream, static_cast<const __nv_bfloat16*>(q),
+  launch_pdl(attn_latent_kernel<MT, PW>, grid, dim3(LA_THREADS + (PW ? 32 * LA_COPY_WARPS : 0)), smem, stream, static_cast<const __nv_bfloat16*>(q),
              static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(pool), block_table, bt_stride, row_start,
              row_pos0, H, dk, dv, scale * 1.4426950408889634f, pages_per_chunk, n_splits, scratch, gate);
   return launch_status("attn_latent");
@@ -401,7 +439,12 @@ using namespace exl3;
 extern "C" int exl3_attn_latent_row_tile(int dk, int max_rows) {
   // the largest tile of rows (in sixteens: 4, 3, 2 or 1) that a sequence's rows fill and whose shared memory fits; 0: none
   const size_t limit = 227 * 1024;
+  static const int most = [] {                               // EXL3_LATENT_TILE=n: at most n sixteens (for measurements)
+    const char* e = getenv("EXL3_LATENT_TILE");
+    return e && e[0] >= '1' && e[0] <= '4' ? e[0] - '0' : 4;
+  }();
   int mt = max_rows > 48 ? 4 : (max_rows > 32 ? 3 : (max_rows > 16 ? 2 : 1));
+  if (mt > most) mt = most;
   while (mt >= 1 && la_smem_bytes(mt, dk) > limit) --mt;
   return mt;
 }
@@ -435,10 +478,10 @@ extern "C" int exl3_attn_latent(const void* q, void* out, const void* pool, cons
   const int max_rows = (int)max_rows64;
   const int mt = exl3_attn_latent_row_tile(dk, max_rows);
   int rc;
-  if (mt == 3) rc = la_launch<3>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
-  else if (mt == 4) rc = la_launch<4>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
-  else if (mt == 2) rc = la_launch<2>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
-  else if (mt == 1) rc = la_launch<1>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
+  if (mt == 3) rc = la_launch<3, false>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
+  else if (mt == 4) rc = la_launch<4, false>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
+  else if (mt == 2) rc = la_launch<2, true>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
+  else if (mt == 1) rc = la_launch<1, true>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
   else { set_error("attn_latent: rows of %d features do not fit shared memory", dk); return ERR_UNSUPPORTED; }
   if (rc) return rc;
   if (n_splits > 1) {
