@@ -15,6 +15,11 @@
 // block takes only the pages of one chunk (chunks are aligned to absolute positions) and leaves a record
 // [dv sums, maximum, sum] per row and chunk, which latent_combine_kernel merges in chunk order.
 //
+// Two forms.  Tiles of three or four sixteens of rows (prompts): the eight warps issue the next page's 16-byte copies
+// themselves.  Tiles of one or two (decoded tokens): four more warps do nothing but copy; they and the eight others
+// hand the two key buffers back and forth through named barriers (2 + buffer: the page has landed; 4 + buffer: the
+// buffer is free again), every one of which each thread of the block reaches the same number of times.
+//
 // Exponentials are base 2: scores carry scale * log2(e), maxima are in those units everywhere.
 #include "api.h"
 #include "common.cuh"
