@@ -25,6 +25,10 @@ from typing import Dict
 
 import numpy as np
 
+from .cache.kv import PAGE_SIZE
+
+SLACK_PAGES = 64
+
 
 class TraceRunner:
     """Applies trace steps to an engine: the request-id -> slot table and
@@ -58,7 +62,8 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time; the cache gets this many and, because every "
+                         "request holds whole pages of 64, 64 pages more")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -68,7 +73,9 @@ def main(argv=None) -> int:
 
     from .engine import Engine
 
-    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens, device=args.device)
+    # a request holds its tokens rounded up to whole pages: room for that rounding of up to 64 live requests
+    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens + SLACK_PAGES * PAGE_SIZE,
+                                device=args.device)
     print("trace_run: ready", file=sys.stderr, flush=True)
     runner = TraceRunner(engine)
     for line in sys.stdin:
