@@ -34,9 +34,9 @@ CONFIGS = {
     # query, two layers reading the same rows, recurrences first and last
     "heads8": RigitarConfig(vocab=300, width=128, norm_eps=1e-6, layers=[
         RigitarLayer("mingru", {"width": 128}, dense(192)),
-        RigitarLayer("latent_attention", latent(8, 16, 32, 16, 64, 96, 0.14, base=50000.0), dense(256)),
-        RigitarLayer("latent_attention", latent(8, 16, 32, 24, 32, 96, 0.14, base=50000.0, kv_from=1), None),
-        RigitarLayer("latent_attention", latent(4, 48, 32, 8, 64, 96, 0.1, base=50000.0, kv_from=1), dense(64)),
+        RigitarLayer("latent_attention", latent(8, 16, 32, 16, 64, 96, 0.14, base=40000.0), dense(256)),
+        RigitarLayer("latent_attention", latent(8, 16, 32, 24, 32, 96, 0.14, base=40000.0, kv_from=1), None),
+        RigitarLayer("latent_attention", latent(4, 48, 32, 8, 64, 96, 0.1, base=40000.0, kv_from=1), dense(64)),
         RigitarLayer("mingru", {"width": 40}, None),
     ]),
     # wide latents (the attention kernel's widest rows), no rotated part at all in one layer, nothing but attention

@@ -62,10 +62,10 @@ def _latent_plain(pool, bt, q, news, ctxs, H, dk, dv, scale, gate=None):
     (16, 576, 512, [1, 1, 1], [300, 64, 1], (1, 1)),            # single tokens, one chunk
     (16, 576, 512, [1, 1, 1], [700, 65, 129], (2, 6)),          # single tokens, chunks of two pages
     (3, 48, 32, [1, 1], [200, 5], (1, 4)),                      # few heads, narrow rows, chunks of one page
-    (40, 144, 128, [1, 1], [130, 257], (2, 3)),                 # more rows than one tile takes
+    (40, 176, 128, [1, 1], [130, 257], (2, 3)),                 # more rows than one tile takes
     (5, 160, 96, [70, 3, 1, 129], [70, 3, 1, 129], (1, 1)),     # prompts from position 0, unequal
     (8, 128, 96, [33, 2], [200, 66], (1, 1)),                   # portions after earlier context
-    (4, 320, 256, [150], [400], (3, 3)),                        # a portion, its keys in chunks
+    (4, 336, 256, [150], [400], (3, 3)),                        # a portion, its keys in chunks
     (2, 592, 512, [40], [40], (1, 1)),                          # the widest rows
 ])
 def test_attention_over_latent_rows_on_the_tensor_cores(H, dk, dv, news, ctxs, chunks):
@@ -86,7 +86,7 @@ def test_attention_over_latent_rows_on_the_tensor_cores(H, dk, dv, news, ctxs, c
 @pytest.mark.parametrize("dtype, tol", [(torch.float32, 2e-6), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("H, dk, dv, news, ctxs", [
     (3, 48, 32, [1, 1], [300, 5]),
-    (8, 144, 128, [40, 2, 1], [90, 300, 1]),
+    (8, 176, 128, [40, 2, 1], [90, 300, 1]),
     (2, 576, 512, [1, 9], [520, 70]),
     (5, 304, 288, [3], [260]),
 ])
@@ -170,7 +170,7 @@ def test_mingru_recurrence_in_both_forms(width, news, dtype):
 
 
 @pytest.mark.parametrize("ydt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T, H", [(1, 100), (7, 2048), (3, 9000), (300, 320)])
+@pytest.mark.parametrize("T, H", [(1, 100), (7, 2048), (3, 9000), (300, 328)])
 def test_output_norm_with_the_residual_sum(T, H, ydt):
     k = K()
     g = torch.Generator().manual_seed(T + H)
@@ -204,7 +204,7 @@ def test_xielu(n, zdt, odt, tol):
     assert float(((got - want).abs() / (want.abs() + z.double().cpu().abs() + 1e-3)).max()) <= tol
 
 
-@pytest.mark.parametrize("M, N, Kf", [(1, 384, 320), (8, 5632, 2048), (16, 70, 96)])
+@pytest.mark.parametrize("M, N, Kf", [(1, 392, 328), (8, 5632, 2048), (16, 70, 88)])
 def test_xielu_as_a_projection_epilogue(M, N, Kf):
     k = K()
     g = torch.Generator().manual_seed(M + N)
