@@ -77,10 +77,13 @@ int exl3_attn_tokens_kv(const void* q, int64_t q_row_stride, void* out, int dtyp
 int exl3_attn_latent_row_tile(int dk, int max_rows);
 size_t exl3_attn_latent_scratch_bytes(int T, int H, int dv, int n_splits);
 // gate (float32 [T * H], or null): a factor per row on the output.
-int exl3_attn_latent(const void* q, void* out, const void* pool, const int* block_table, int bt_stride,
+// pool_pages: pages in the pool (its rows are pool_pages * 64).  exl3_attn_latent_status() returns and clears the flag a
+// block left when a bounded wait for a page's copies ran out.
+int exl3_attn_latent(const void* q, void* out, const void* pool, int64_t pool_pages, const int* block_table, int bt_stride,
                      const int* row_start, const int* row_pos0, int B, int T, int max_new, int H, int dk, int dv, int page,
                      float scale, int pages_per_chunk, int n_splits, float* scratch, size_t scratch_bytes,
                      const float* gate, cudaStream_t stream);
+int exl3_attn_latent_status();
 
 // Residual update with the norm on the sublayer's output: h[t,:] += y[t,:] * rsqrt(mean(y[t,:]^2) + eps) * w (skipped
 // when y is null), then x[t,:] = h[t,:] in x_dtype (skipped when x is null).  Statistics and the sum are float32.

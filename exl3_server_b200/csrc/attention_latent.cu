@@ -7,7 +7,7 @@
 //
 // One kernel serves prompts, portions of prompts and single tokens.  A block of eight warps takes a tile of
 // 16 * MT consecutive rows of one sequence and walks the sequence's pages (64 keys, one page a step, the next page
-// on its way by cp.async while this one is worked on).  All warps share all rows: for the scores a warp owns 8 of
+// on its way while this one is worked on).  All warps share all rows: for the scores a warp owns 8 of
 // the page's 64 keys (its B fragments serve every row tile), for the output it owns every eighth 16-column slice
 // of the values (its B fragments, read transposed out of the very tile the keys came from, again serve every row
 // tile).  Row maxima and sums meet in shared memory; the running maximum, the running sum and the output
@@ -15,15 +15,15 @@
 // block takes only the pages of one chunk (chunks are aligned to absolute positions) and leaves a record
 // [dv sums, maximum, sum] per row and chunk, which latent_combine_kernel merges in chunk order.
 //
-// Two forms.  Tiles of three or four sixteens of rows (prompts): the eight warps issue the next page's 16-byte copies
-// themselves.  Tiles of one or two (decoded tokens): four more warps do nothing but copy; they and the eight others
-// hand the two key buffers back and forth through named barriers (2 + buffer: the page has landed; 4 + buffer: the
-// buffer is free again), every one of which each thread of the block reaches the same number of times.
+// A page of keys comes as TMA tile copies (boxes of 64 keys x 64 features, 128-byte swizzle, which ldmatrix then
+// follows) that one thread asks for a page ahead; they report to an mbarrier per buffer, and every wait on one is
+// bounded (a block that gives up sets a flag for the host, exl3_attn_latent_status, and leaves).
 //
 // Exponentials are base 2: scores carry scale * log2(e), maxima are in those units everywhere.
 #include "api.h"
 #include "common.cuh"
 
+#include <cuda.h>
 #include <math.h>
 #include <stdlib.h>
 
@@ -33,7 +33,6 @@ constexpr int LA_WARPS = 8;
 constexpr int LA_THREADS = LA_WARPS * 32;
 constexpr int LA_KEYS = 64;                // keys per step: one page
 constexpr int LA_PAD = 8;                  // elements added to a shared-memory row: 16-byte pieces of consecutive rows fall into different banks
-constexpr int LA_COPY_WARPS = 4;           // warps that only copy pages, in the kernel's form that has them
 constexpr int LA_MAX_PAIRS = 4;            // 16-column slices of the values per warp: dv <= 8 * 4 * 16 = 512
 
 __device__ inline void la_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
@@ -41,53 +40,69 @@ __device__ inline void la_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
-__device__ inline void la_ldmatrix_x2(uint32_t (&r)[2], const void* p) {
-  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
-}
-__device__ inline void la_ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
-  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
-}
 __device__ inline void la_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ inline void la_cp_async16(void* dst, const void* src) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
-}
-__device__ inline void la_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ inline void la_cp_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-__device__ inline void la_bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
-__device__ inline void la_bar_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 __device__ inline float la_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
-// PW: four more warps do nothing but copy the pages (see the top of the file); the eight others then meet at named
-// barriers: 1 among themselves, 2 + buffer when a page has landed, 4 + buffer when they are done with it.
-template <int MT, bool PW>
-__global__ void __launch_bounds__(LA_THREADS + (PW ? 32 * LA_COPY_WARPS : 0), 1)
-attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat16* pool, const int* __restrict__ block_table,
-                   int bt_stride, const int* __restrict__ row_start, const int* __restrict__ row_pos0, int H, int dk, int dv,
-                   float scale_log2, int pages_per_chunk, int n_splits, float* scratch, const float* gate) {
+// Bounded wait for a page's copies (false when they did not land within the limit; the host reads the flag).
+constexpr uint32_t LA_WAIT_LIMIT = 1u << 24;
+static __device__ int g_la_error = 0;
+__device__ inline uint32_t la_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ inline bool la_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < LA_WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+// Address of the 16-byte piece that holds (key row, feature col) of a key tile as the copies lay it out: boxes of 64
+// features, 8 KB each, a row of a box 128 bytes, its 16-byte pieces swizzled by the row (128-byte swizzle).
+__device__ inline uint32_t la_key_addr(uint32_t tile, int row, int col) {
+  return tile + (uint32_t)(col >> 6) * 8192u + (uint32_t)row * 128u + (uint32_t)((((col >> 3) & 7) ^ (row & 7)) << 4);
+}
+__device__ inline void la_ldsm_x2(uint32_t (&r)[2], uint32_t a) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ inline void la_ldsm_x4_trans(uint32_t (&r)[4], uint32_t a) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+template <int MT>
+__global__ void __launch_bounds__(LA_THREADS, 1)
+attn_latent_kernel(const __grid_constant__ CUtensorMap map_k, const __nv_bfloat16* q, __nv_bfloat16* out,
+                   const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
+                   const int* __restrict__ row_pos0, int H, int dk, int dv, float scale_log2, int pages_per_chunk,
+                   int n_splits, float* scratch, const float* gate) {
   constexpr int M = 16 * MT;
-  extern __shared__ __align__(16) unsigned char la_smem[];
-  const int ldk = dk + LA_PAD;                      // elements per shared-memory row of Q and K
+  extern __shared__ unsigned char la_smem_raw[];
+  const int ldk = dk + LA_PAD;                      // elements per shared-memory row of Q
   constexpr int ldp = LA_KEYS + LA_PAD;
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(la_smem);
-  __nv_bfloat16* Ks = Qs + (size_t)M * ldk;         // two tiles of LA_KEYS rows
-  __nv_bfloat16* Ps = Ks + (size_t)2 * LA_KEYS * ldk;
+  const int boxes = (dk + 63) >> 6;                 // copies per page: 64 keys x 64 features each
+  const uint32_t tile_bytes = (uint32_t)boxes * 8192u;
+  // two key tiles first, on a 1 KB boundary (the swizzle's unit); then Q, P, the statistics, two mbarriers
+  unsigned char* base = la_smem_raw + ((1024u - (la_u32(la_smem_raw) & 1023u)) & 1023u);
+  const uint32_t Ks = la_u32(base);
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(base + 2 * (size_t)tile_bytes);
+  __nv_bfloat16* Ps = Qs + (size_t)M * ldk;
   float* red_max = reinterpret_cast<float*>(Ps + (size_t)M * ldp);   // [LA_WARPS][M]
   float* red_sum = red_max + LA_WARPS * M;          // [LA_WARPS][M]
   float* m_run = red_sum + LA_WARPS * M;            // [M]
   float* l_run = m_run + M;                         // [M]
   float* corr = l_run + M;                          // [M]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(corr + M + (M & 1));  // [2], 8-byte aligned
 
   pdl_wait();
   pdl_trigger();
@@ -108,49 +123,27 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
   const int* bt = block_table + (int64_t)b * bt_stride;
   const int vecs = dk / 8;                                   // 16-byte pieces per row
 
-  constexpr int ALL = LA_THREADS + 32 * LA_COPY_WARPS;              // the threads that meet at the barriers between the copying warp and the others
-  auto sync_compute = [&]() {
-    if constexpr (PW) la_bar_sync(1, LA_THREADS); else __syncthreads();
+  // One thread asks for a page: `boxes` tile copies that report their bytes to the buffer's mbarrier.  A page that
+  // is not there (never the case for a key that a row sees) reads page 0; features beyond dk come as zeros.
+  auto ask = [&](int pg, int buf) {
+    const uint32_t bar = la_u32(bars + buf);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tile_bytes) : "memory");
+    const int row0 = (pg < 0 ? 0 : pg) * LA_KEYS;
+    for (int j = 0; j < boxes; ++j)
+      asm volatile(
+          "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+          ::"r"(Ks + (uint32_t)buf * tile_bytes + (uint32_t)j * 8192u), "l"(&map_k), "r"(bar), "r"(j * 64), "r"(row0)
+          : "memory");
   };
-  // a thread's pieces of a key tile: piece i = index + copiers * n lies in row r(n), column c(n), stepped without dividing
-  constexpr int COPIERS = PW ? 32 * LA_COPY_WARPS : LA_THREADS;
-  const int ci = PW ? tid - LA_THREADS : tid;         // (meaningful in the copying warps only when there are such)
-  const int step_r = COPIERS / vecs, step_c = COPIERS % vecs;
-  const int first_r = ci / vecs, first_c = ci % vecs;
-  auto load_keys = [&](int pg, int buf) {
-    __nv_bfloat16* dst = Ks + (size_t)buf * LA_KEYS * ldk;
-    int r = first_r, c = first_c;
-    while (r < LA_KEYS) {
-      if (pg >= 0) la_cp_async16(dst + (size_t)r * ldk + c * 8, pool + ((int64_t)pg * LA_KEYS + r) * dk + c * 8);
-      else *reinterpret_cast<uint4*>(dst + (size_t)r * ldk + c * 8) = make_uint4(0, 0, 0, 0);
-      r += step_r;
-      c += step_c;
-      if (c >= vecs) { c -= vecs; ++r; }
-    }
-  };
-  // page numbers are fetched one step before the copy that needs them, so that no copy waits for its address
-  int pg_next = page_lo <= page_hi ? __ldcg(bt + page_lo) : -1;
-  if constexpr (PW) {
-    if (warp >= LA_WARPS) {
-      // the copying warp: a page into the buffer that the others have let go of, then the word that it has landed
-      for (int pi = page_lo; pi <= page_hi; ++pi) {
-        const int buf = (pi - page_lo) & 1;
-        const int pg = pg_next;
-        pg_next = pi + 1 <= page_hi ? __ldcg(bt + pi + 1) : -1;
-        if (pi - page_lo >= 2) la_bar_sync(4 + buf, ALL);
-        load_keys(pg, buf);
-        la_cp_commit();
-        la_cp_wait_all();
-        __threadfence_block();
-        la_bar_arrive(2 + buf, ALL);
-      }
-      return;
-    }
-  } else {
-    if (page_lo <= page_hi) load_keys(pg_next, 0);
-    la_cp_commit();
-    pg_next = page_lo + 1 <= page_hi ? __ldcg(bt + page_lo + 1) : -1;
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(la_u32(bars)));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(la_u32(bars + 1)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (page_lo <= page_hi) ask(__ldcg(bt + page_lo), 0);
   }
+  // page numbers are fetched one step before the copies that need them
+  int pg_next = (tid == 0 && page_lo + 1 <= page_hi) ? __ldcg(bt + page_lo + 1) : -1;
   // the queries of the tile; rows beyond the sequence's are zero
   for (int i = tid; i < M * vecs; i += LA_THREADS) {
     const int r = i / vecs, c = (i - r * vecs) * 8;
@@ -159,7 +152,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
     *reinterpret_cast<uint4*>(Qs + (size_t)r * ldk + c) = v;
   }
   if (tid < M) { m_run[tid] = -INFINITY; l_run[tid] = 0.0f; }
-  if constexpr (PW) sync_compute();                          // (without a copying warp the loop's first barrier does this)
+  __syncthreads();                                           // Q, the statistics and the mbarriers are set up
 
   float o[MT][LA_MAX_PAIRS][2][4];
 #pragma unroll
@@ -178,19 +171,18 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
   const int a_row = lane & 15, a_col = (lane >> 4) * 8;
   const int bk_row = warp * 8 + (lane & 7), bk_col = ((lane >> 3) & 1) * 8;
   const int bv_row = (lane & 7) + ((lane >> 3) & 1) * 8, bv_col = (lane >> 4) * 8;
+  bool fine = true;
 
   for (int pi = page_lo; pi <= page_hi; ++pi) {
     const int buf = (pi - page_lo) & 1;
-    if constexpr (PW) {
-      la_bar_sync(2 + buf, ALL);                             // this page's keys have landed
-    } else {
-      la_cp_wait_all();
-      __syncthreads();                                       // this page's keys (and, the first time, Q) are in place
-      if (pi + 1 <= page_hi) load_keys(pg_next, buf ^ 1);    // that buffer's last readers passed the barrier above
-      la_cp_commit();
+    // this page's keys have landed (every thread looks for itself; the block then agrees on what it saw)
+    const bool landed = la_mbar_wait(la_u32(bars + buf), ((pi - page_lo) >> 1) & 1);
+    if (!__syncthreads_and(landed)) { fine = false; break; }
+    if (tid == 0 && pi + 1 <= page_hi) {
+      ask(pg_next, buf ^ 1);                                 // that buffer's last readers passed the page's last barrier
       pg_next = pi + 2 <= page_hi ? __ldcg(bt + pi + 2) : -1;
     }
-    const __nv_bfloat16* Kt = Ks + (size_t)buf * LA_KEYS * ldk;
+    const uint32_t Kt = Ks + (uint32_t)buf * tile_bytes;
 
     // scores of all rows against this warp's 8 keys
     // (with few row tiles the features go round KS sums per tile, so that the chain of dependent products is short)
@@ -208,7 +200,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
       for (int u = 0; u < KS; ++u) {
         const int kk = k0 + 16 * u;
         if (kk < dk) {
-          la_ldmatrix_x2(bfr[which][u], Kt + (size_t)bk_row * ldk + kk + bk_col);
+          la_ldsm_x2(bfr[which][u], la_key_addr(Kt, bk_row, kk + bk_col));
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) la_ldmatrix_x4(afr[which][u][mt], Qs + (size_t)(mt * 16 + a_row) * ldk + kk + a_col);
         }
@@ -257,7 +249,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
         if ((lane & 3) == 0) red_max[warp * M + r] = mx;
       }
     }
-    sync_compute();
+    __syncthreads();
     if (tid < M) {
       float mx = red_max[tid];
 #pragma unroll
@@ -266,7 +258,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
       corr[tid] = mn == -INFINITY ? 1.0f : la_exp2(mo - mn);      // exp2(-inf) = 0 the first time
       m_run[tid] = mn;
     }
-    sync_compute();
+    __syncthreads();
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -284,7 +276,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
         if ((lane & 3) == 0) red_sum[warp * M + r] = sm;
       }
     }
-    sync_compute();
+    __syncthreads();
     if (tid < M) {
       float sm = 0.0f;
 #pragma unroll
@@ -311,7 +303,7 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
 #pragma unroll
       for (int i = 0; i < LA_MAX_PAIRS; ++i) {
         const int col = (warp + LA_WARPS * i) * 16;
-        if (col < dv) la_ldmatrix_x4_trans(vf[i], Kt + (size_t)(kk + bv_row) * ldk + col + bv_col);
+        if (col < dv) la_ldsm_x4_trans(vf[i], la_key_addr(Kt, kk + bv_row, col + bv_col));
       }
 #pragma unroll
       for (int i = 0; i < LA_MAX_PAIRS; ++i) {
@@ -325,13 +317,12 @@ attn_latent_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat
         }
       }
     }
-    if constexpr (PW) {
-      if (pi + 2 <= page_hi) la_bar_arrive(4 + buf, ALL);    // the copying warp may fill this buffer again
-    }
-    sync_compute();                                          // P, the statistics and (without a copying warp) this key tile are free again
+    __syncthreads();                                         // P, the statistics and this key tile are free again
   }
-  la_cp_wait_all();
-  sync_compute();                                            // the statistics, also when the chunk held no page
+  if (!fine) {
+    if (tid == 0) atomicExch(&g_la_error, 1);                // the host reads this; the rows get what was summed so far
+  }
+  __syncthreads();                                           // the statistics, also when the chunk held no page
 
   // results: rows qr and qr + 8 of every row tile, this warp's column slices
 #pragma unroll
@@ -416,24 +407,54 @@ __global__ void latent_combine_kernel(const float* __restrict__ scratch, __nv_bf
 
 static size_t la_smem_bytes(int MT, int dk) {
   const size_t M = 16 * (size_t)MT;
-  return ((M + 2 * LA_KEYS) * (dk + LA_PAD) + M * (LA_KEYS + LA_PAD)) * sizeof(__nv_bfloat16) +
-         (2 * LA_WARPS * M + 3 * M) * sizeof(float);
+  const size_t tile = (size_t)((dk + 63) / 64) * 8192;       // a page of keys: boxes of 64 x 64
+  return 1024 + 2 * tile + (M * (dk + LA_PAD) + M * (LA_KEYS + LA_PAD)) * sizeof(__nv_bfloat16) +
+         (2 * LA_WARPS * M + 3 * M + 2) * sizeof(float) + 2 * sizeof(uint64_t);
 }
 
-template <int MT, bool PW>
-static int la_launch(const void* q, void* out, const void* pool, const int* block_table, int bt_stride, const int* row_start,
-                     const int* row_pos0, int B, int max_rows, int H, int dk, int dv, float scale, int pages_per_chunk,
-                     int n_splits, float* scratch, const float* gate, cudaStream_t stream) {
+typedef CUresult (*LaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static LaEncodeFn la_encode_fn() {
+  static LaEncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<LaEncodeFn>(p);
+  }();
+  return fn;
+}
+// The pool as [pages * 64 rows, dk features] bfloat16; boxes of 64 features x 64 rows, 128-byte swizzle, zeros beyond dk.
+static int la_make_map(CUtensorMap* map, const void* pool, int64_t rows, int dk) {
+  LaEncodeFn fn = la_encode_fn();
+  if (!fn) { set_error("attn_latent: the driver has no cuTensorMapEncodeTiled"); return ERR_UNSUPPORTED; }
+  const cuuint64_t dims[2] = {(cuuint64_t)dk, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)dk * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)LA_KEYS};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("attn_latent: cuTensorMapEncodeTiled failed with %d", (int)r); return ERR_BAD_ARGUMENT; }
+  return 0;
+}
+
+template <int MT>
+static int la_launch(const CUtensorMap& map, const void* q, void* out, const int* block_table, int bt_stride,
+                     const int* row_start, const int* row_pos0, int B, int max_rows, int H, int dk, int dv, float scale,
+                     int pages_per_chunk, int n_splits, float* scratch, const float* gate, cudaStream_t stream) {
   const size_t smem = la_smem_bytes(MT, dk);
-  cudaError_t e = cudaFuncSetAttribute(attn_latent_kernel<MT, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(attn_latent_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("attn_latent: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
     return (int)e;
   }
   dim3 grid(ceil_div(max_rows, 16 * MT), B, n_splits);
-  launch_pdl(attn_latent_kernel<MT, PW>, grid, dim3(LA_THREADS + (PW ? 32 * LA_COPY_WARPS : 0)), smem, stream, static_cast<const __nv_bfloat16*>(q),
-             static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(pool), block_table, bt_stride, row_start,
-             row_pos0, H, dk, dv, scale * 1.4426950408889634f, pages_per_chunk, n_splits, scratch, gate);
+  launch_pdl(attn_latent_kernel<MT>, grid, dim3(LA_THREADS), smem, stream, map, static_cast<const __nv_bfloat16*>(q),
+             static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, H, dk, dv,
+             scale * 1.4426950408889634f, pages_per_chunk, n_splits, scratch, gate);
   return launch_status("attn_latent");
 }
 
@@ -458,13 +479,21 @@ extern "C" size_t exl3_attn_latent_scratch_bytes(int T, int H, int dv, int n_spl
   return n_splits <= 1 ? 0 : (size_t)T * H * n_splits * (dv + 2) * sizeof(float);
 }
 
-extern "C" int exl3_attn_latent(const void* q, void* out, const void* pool, const int* block_table, int bt_stride,
+// 1 when a block gave up waiting for a page's copies since the last call (its rows are then not to be trusted); clears it.
+extern "C" int exl3_attn_latent_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_la_error, sizeof(int));
+  if (v) { int z = 0; cudaMemcpyToSymbol(g_la_error, &z, sizeof(int)); }
+  return v;
+}
+
+extern "C" int exl3_attn_latent(const void* q, void* out, const void* pool, int64_t pool_pages, const int* block_table, int bt_stride,
                                 const int* row_start, const int* row_pos0, int B, int T, int max_new, int H, int dk, int dv,
                                 int page, float scale, int pages_per_chunk, int n_splits, float* scratch,
                                 size_t scratch_bytes, const float* gate, cudaStream_t stream) {
   if (B == 0 || T == 0) return 0;
   if (B < 0 || T < 0 || max_new < 1 || H < 1 || dk < 16 || dk % 16 != 0 || dv < 16 || dv % 16 != 0 || dv > dk ||
-      dv > LA_WARPS * LA_MAX_PAIRS * 16 || page != LA_KEYS || n_splits < 1 || n_splits > 65535 ||
+      dv > LA_WARPS * LA_MAX_PAIRS * 16 || page != LA_KEYS || n_splits < 1 || n_splits > 65535 || pool_pages < 1 ||
       (n_splits > 1 && pages_per_chunk < 1)) {
     set_error("attn_latent: bad sizes rows=%d tokens=%d heads=%d dk=%d dv=%d (multiples of 16, dv <= dk, dv <= %d) "
               "page=%d (must be %d) splits=%d", B, T, H, dk, dv, LA_WARPS * LA_MAX_PAIRS * 16, page, LA_KEYS, n_splits);
@@ -482,12 +511,17 @@ extern "C" int exl3_attn_latent(const void* q, void* out, const void* pool, cons
   if (max_rows64 > 0x7fffffffLL || B > 65535) { set_error("attn_latent: grid too large"); return ERR_UNSUPPORTED; }
   const int max_rows = (int)max_rows64;
   const int mt = exl3_attn_latent_row_tile(dk, max_rows);
-  int rc;
-  if (mt == 3) rc = la_launch<3, false>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
-  else if (mt == 4) rc = la_launch<4, false>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
-  else if (mt == 2) rc = la_launch<2, true>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
-  else if (mt == 1) rc = la_launch<1, true>(q, out, pool, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, pages_per_chunk, n_splits, scratch, gate, stream);
+  CUtensorMap map;
+  int rc = la_make_map(&map, pool, pool_pages * LA_KEYS, dk);
+  if (rc) return rc;
+#define EXL3_LA(MT) la_launch<MT>(map, q, out, block_table, bt_stride, row_start, row_pos0, B, max_rows, H, dk, dv, scale, \
+                                  pages_per_chunk, n_splits, scratch, gate, stream)
+  if (mt == 4) rc = EXL3_LA(4);
+  else if (mt == 3) rc = EXL3_LA(3);
+  else if (mt == 2) rc = EXL3_LA(2);
+  else if (mt == 1) rc = EXL3_LA(1);
   else { set_error("attn_latent: rows of %d features do not fit shared memory", dk); return ERR_UNSUPPORTED; }
+#undef EXL3_LA
   if (rc) return rc;
   if (n_splits > 1) {
     if (B > 65535) { set_error("attn_latent: too many sequences for the merge"); return ERR_UNSUPPORTED; }

@@ -519,6 +519,11 @@ def attn_latent_supported(dtype: torch.dtype, dk: int, dv: int, page: int) -> bo
             and int(library().exl3_attn_latent_row_tile(_c_int(dk), _c_int(16))) >= 1)
 
 
+def attn_latent_status() -> int:
+    """1 when a block of the latent attention kernel gave up on a bounded wait since the last call; clears it."""
+    return int(library().exl3_attn_latent_status())
+
+
 def attn_latent_row_tile(dk: int, max_rows: int) -> int:
     """Rows of one sequence that a block of the kernel takes for these sizes."""
     return 16 * int(library().exl3_attn_latent_row_tile(_c_int(dk), _c_int(max_rows)))
@@ -540,9 +545,11 @@ def attn_latent(q: torch.Tensor, out: torch.Tensor, pool: torch.Tensor, block_ta
         raise KernelLibraryError("attn_latent: q, out and the cache must be bfloat16")
     _contig(q, "q")
     _contig(out, "out")
+    _contig(pool, "pool")
     nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
     _check(library().exl3_attn_latent(
-        _ptr(q), _ptr(out), _ptr(pool), _ptr(block_table), _c_int(block_table.stride(0)), _ptr(row_start),
+        _ptr(q), _ptr(out), _ptr(pool), _c_int64(pool.numel() // (64 * dk)), _ptr(block_table),
+        _c_int(block_table.stride(0)), _ptr(row_start),
         _ptr(row_pos0), _c_int(rows), _c_int(T), _c_int(max_new), _c_int(heads), _c_int(dk), _c_int(dv), _c_int(page),
         _c_float(scale), _c_int(pages_per_chunk), _c_int(n_splits), _ptr(scratch), _c_size_t(nbytes), _ptr(gate),
         _stream()), "attn_latent")
@@ -759,7 +766,8 @@ def check_status() -> None:
     gave_up = [name for name, fn in (("gemm_tc", gemm_tc_status), ("gemm_skinny", gemm_skinny_status),
                                      ("gemm_pair", gemm_pair_status),
                                      ("attn_prefill_tc", attn_prefill_tc_status),
-                                     ("attn_decode", attn_decode_status)) if fn()]
+                                     ("attn_decode", attn_decode_status),
+                                     ("attn_latent", attn_latent_status)) if fn()]
     if gave_up:
         raise KernelLibraryError("a bounded wait ran out in " + ", ".join(gave_up) +
                                  ": a copy or a tensor-core product did not complete in time")
