@@ -138,17 +138,18 @@ class LatentAttention:
                     self.kv_rank, rot_dim=self.rot_dim, rot=self.rot, inv_freq=self.inv_freq, tok_pos=batch.tok_pos,
                     tail_off=self.rank_pad)
         if many:
-            ql.view(T, H, self.row)[:, :, :self.kv_rank] = torch.bmm(
-                q.view(T, H, hq)[:, :, :self.dim].transpose(0, 1), self.w_uk).transpose(0, 1)
+            # a product per head, written where the head's row of ql has its place (a strided view: no copy afterwards)
+            torch.bmm(q.view(T, H, hq)[:, :, :self.dim].transpose(0, 1), self.w_uk,
+                      out=ql.view(T, H, self.row)[:, :, :self.kv_rank].transpose(0, 1))
         ol = torch.empty((T, H * self.rank_pad), dtype=dt, device=x.device)
         gated = self.attend(ql, ol, batch, kv, gate)
+        o = torch.empty((T, H * self.vdim), dtype=dt, device=x.device)
         if many:
-            o = torch.bmm(ol.view(T, H, self.rank_pad)[:, :, :self.kv_rank].transpose(0, 1), self.w_uv)
-            o = o.transpose(0, 1).reshape(T, H * self.vdim)
+            torch.bmm(ol.view(T, H, self.rank_pad)[:, :, :self.kv_rank].transpose(0, 1), self.w_uv,
+                      out=o.view(T, H, self.vdim).transpose(0, 1))
             if not gated:
                 o = (o.view(T, H, self.vdim) * gate[:, :, None]).to(dt).view(T, H * self.vdim)
         else:
-            o = torch.empty((T, H * self.vdim), dtype=dt, device=x.device)
             K.head_gemm(ol, H * self.rank_pad, self.rank_pad, self.w_uv, o, H * self.vdim, self.vdim, T, H,
                         self.kv_rank, self.vdim, mul=None if gated else gate)
         return self.o(o, out_dtype=self.o.wide_dtype(T))
