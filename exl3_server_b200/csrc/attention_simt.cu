@@ -385,6 +385,7 @@ static int dispatch(const void* q, int64_t q_row_stride, void* out, const void* 
     if (G == 1 || VEC == 8) EXL3_ATT(1, 5);
     EXL3_ATT(2, 5);
   }
+  if (R <= 8) EXL3_ATT(1, 8);                         // rows of up to 1,024 (float32) or 2,048 (bfloat16) features: a head a pass
 #undef EXL3_ATT
   set_error("attn_tokens: head_dim %d is too large for this kernel", hd);
   return ERR_UNSUPPORTED;

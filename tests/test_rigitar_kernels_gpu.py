@@ -89,6 +89,7 @@ def test_attention_over_latent_rows_on_the_tensor_cores(H, dk, dv, news, ctxs, c
     (8, 176, 128, [40, 2, 1], [90, 300, 1]),
     (2, 576, 512, [1, 9], [520, 70]),
     (5, 304, 288, [3], [260]),
+    (2, 832, 768, [1, 5], [130, 70]),                  # rows wider than anything the tensor-core kernel takes
 ])
 def test_attention_over_latent_rows_on_the_cuda_cores(H, dk, dv, news, ctxs, dtype, tol):
     k = K()
