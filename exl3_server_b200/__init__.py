@@ -7,12 +7,12 @@ Entry points::
     results = generate(engine, prompts=[[1, 2, 3]], options=GenerateOptions(max_tokens=16))
 """
 from . import models  # noqa: F401  (registers the architectures)
-from .config import ConfigError, LlamaConfig, RigitarConfig, register_architecture, resolve_architecture
+from .config import ConfigError, LlamaConfig, NikodraConfig, RigitarConfig, register_architecture, resolve_architecture
 from .engine import (Engine, GenerateOptions, GenerateResult, Model, StepEntry, StepError, generate,
                      load_model)
 from .sampling import SampleOptions
 from .weights import WeightsError
 from .weights.random_init import write_random_model
 
-__all__ = ["ConfigError", "LlamaConfig", "RigitarConfig", "register_architecture", "resolve_architecture", "Engine", "Model", "GenerateOptions", "GenerateResult", "SampleOptions", "generate",
+__all__ = ["ConfigError", "LlamaConfig", "RigitarConfig", "NikodraConfig", "register_architecture", "resolve_architecture", "Engine", "Model", "GenerateOptions", "GenerateResult", "SampleOptions", "generate",
            "StepEntry", "StepError", "load_model", "WeightsError", "write_random_model"]

@@ -96,9 +96,11 @@ class KVGroup:
         """Logical pages below this hold no key that a query at position
         ``length`` or later can see."""
         w = self.request.window
-        if w <= 0:
-            return 0
-        return max(0, length - w + 1) // self.page_size
+        first = max(0, length - w + 1) if w > 0 else 0
+        c = self.request.chunk
+        if c > 0:
+            first = max(first, length // c * c)        # the block of positions that holds ``length``
+        return first // self.page_size
 
 
 class SequenceCache:
@@ -110,7 +112,8 @@ class SequenceCache:
 
     def __init__(self, requests: Sequence[Tuple[Optional[KVRequest], Optional[StateRequest], Optional[int]]],
                  max_tokens: int, dtype: torch.dtype = torch.bfloat16, device="cpu",
-                 page_size: int = PAGE_SIZE, max_slots: Optional[int] = None, allocate: bool = True):
+                 page_size: int = PAGE_SIZE, max_slots: Optional[int] = None, allocate: bool = True,
+                 extra_states: Optional[Dict[str, StateRequest]] = None):
         if max_tokens < 1:
             raise CacheError(f"max_tokens must be positive, got {max_tokens}")
         self.page_size = page_size
@@ -139,6 +142,9 @@ class SequenceCache:
                     if src_req.window > 0 and not 0 < kv.window <= src_req.window:
                         raise CacheError(f"schedule entry {i} (window {kv.window or 'none'}) cannot read entry "
                                          f"{src}'s cache, which keeps only a window of {src_req.window}")
+                    if src_req.chunk > 0 and kv.chunk != src_req.chunk:
+                        raise CacheError(f"schedule entry {i} cannot read entry {src}'s cache, which keeps only "
+                                         f"the current block of {src_req.chunk} positions")
                 self.entry_group.append(self.entry_group[src])
                 self.entry_owns.append(False)
                 continue
@@ -155,12 +161,16 @@ class SequenceCache:
             g.owners.append(i)
         self.state: Dict[int, torch.Tensor] = {}
         self._state_requests = {i: s for i, (_kv, s, _src) in enumerate(requests) if s is not None}
+        # state that belongs to no schedule entry (an embedding that looks at the token before), under its owner's key
+        self._state_requests.update(extra_states or {})
         if allocate:
             for g in self.groups:
                 g.allocate(dtype, device)
             for i, s in self._state_requests.items():
-                # one row more than there are slots, for rows that only pad a batch
-                self.state[i] = torch.zeros((self.slots.n_slots + 1, *s.shape), dtype=s.dtype, device=device)
+                # one row more than there are slots, for rows that only pad a batch; an owner that asks for
+                # several tensors (a tuple of requests) gets a tuple
+                make = lambda r: torch.zeros((self.slots.n_slots + 1, *r.shape), dtype=r.dtype, device=device)
+                self.state[i] = tuple(make(r) for r in s) if isinstance(s, (tuple, list)) else make(s)
 
     @property
     def pad_page(self) -> int:
@@ -178,7 +188,8 @@ class SequenceCache:
         for g in self.groups:
             g.pages[slot] = []
         for t in self.state.values():
-            t[slot].zero_()
+            for part in (t if isinstance(t, tuple) else (t,)):
+                part[slot].zero_()
         return slot
 
     def close(self, slot: int) -> None:
@@ -274,7 +285,8 @@ class SequenceCache:
         g = self.groups[gi]
         return KVLayerView(g.k[li], g.v[li], block_tables[gi], self.page_size, self.entry_owns[entry])
 
-    def state_of(self, entry: int) -> Optional[torch.Tensor]:
+    def state_of(self, entry) -> Optional[torch.Tensor]:
+        """The state tensor ``[slots + 1, *shape]`` of a schedule entry (by index) or of another owner (by key)."""
         return self.state.get(entry)
 
     # -- accounting ----------------------------------------------------------

@@ -68,6 +68,67 @@ int exl3_attn_tokens_kv(const void* q, int64_t q_row_stride, void* out, int dtyp
                         float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
                         cudaStream_t stream);
 
+// The general form: the value pool has a row pitch of its own (v_row >= hdv; hd, hdv and both pitches multiples of 8,
+// values may be wider than keys); chunk > 0 also hides every key before floor(pos / chunk) * chunk; sink != 0 adds
+// one to the softmax's denominator (a key of score 0 without a value).
+int exl3_attn_tokens_ex(const void* q, int64_t q_row_stride, void* out, int dtype, const void* k_pool,
+                        const void* v_pool, const int* block_table, int bt_stride, const int* tok_pos,
+                        const int* tok_seq, int T, int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page,
+                        int window, int chunk, int sink, float scale, int split_keys, int max_splits, float* scratch,
+                        size_t scratch_bytes, cudaStream_t stream);
+
+// Token embedding plus a row of a second table picked by a hash of (previous token, token):
+//   h[t] = table[id_t] + extra[(prev_t * mul_prev + id_t * mul_cur) mod buckets],  extra[buckets] for position 0.
+// The previous token of a row's first token in this step comes from last_token[slot] (int32 per slot), which the
+// kernel then sets to the row's last token of the step.  Sums are float32.
+int exl3_embed_hashed(const int* ids, const int* tok_pos, const int* tok_seq, const int* row_start,
+                      const int* slot_ids, const void* table, const void* extra, int dtype, int buckets,
+                      long long mul_prev, long long mul_cur, int* last_token, float* h, int T, int H, int V,
+                      cudaStream_t stream);
+
+// The step between an attention's joint input projection and the attention itself (see qk_prep.cu).
+//   x [T, ld] holds per token nh query heads (at q_off), nkv key heads (k_off) of hd features and nkv value heads
+//   (v_off, or < 0 for none) of hdv features.  norm: 0 none, 1 divide a query/key head by its root mean square,
+//   2 the same times q_w / k_w [hd].  rot > 0: rotary encoding of the first rot features (layout 0: feature i with
+//   i + rot / 2; 1: feature 2i with 2i + 1), sines and cosines times mscale.  Keys are then multiplied by k_mul.
+//   mix_lambda != null: v <- (1 - lambda) v + lambda v_src[t] (v_src [T, v_src_ld], its own type).
+//   Queries go to q_out [T, nh * hd_pad]; keys and values to the paged cache (k_pool / v_pool, rows of hd_pad /
+//   hdv_pad features, pad features zero), or, when k_pool is null, keys to k_out [T, nkv * hd_pad].
+int exl3_qk_prep(const void* x, int x_dtype, int64_t ld, int q_off, int k_off, int v_off, int T, int nh, int nkv,
+                 int hd, int hdv, int hd_pad, int hdv_pad, int norm, const void* q_w, const void* k_w, int w_dtype,
+                 float eps, int rot, int layout, const float* inv_freq, const float* inv_freq_lo, float mscale,
+                 float k_mul, const void* mix_lambda, int lambda_dtype, const void* v_src, int v_src_dtype,
+                 int64_t v_src_ld, const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
+                 int page, void* q_out, int q_out_dtype, void* k_out, int k_out_dtype, void* k_pool, void* v_pool,
+                 int pool_dtype, cudaStream_t stream);
+
+// Token shift: for s < n_mix, out[s][t] = h[t] + (h[t - 1] - h[t]) * mu[s]; the row before a row's first token of
+// this step comes from prev[slot] (float32 [slots, H], zero for a new sequence), which is then set to the row's last
+// h of the step.
+int exl3_token_shift(const void* h, int h_dtype, const void* mu, int mu_dtype, int n_mix, float* prev,
+                     const int* tok_seq, const int* row_start, const int* slot_ids, void* out, int out_dtype, int T,
+                     int H, cudaStream_t stream);
+
+// A linear recurrence with a matrix state per head (float32 [slots, heads, dk, dv]); see linear_scan.cu.
+//   mode 0 (decay per token and key channel, bonus for the current token):
+//     o_t = S^T r_t + (sum_i r_ti u_i k_ti) v_t,   S <- diag(w_t) S + k_t v_t^T,  w_t = exp(-exp(wraw_t + w0))
+//   mode 1 (one decay per head): S <- decay_h S + k_t v_t^T,  o_t = S^T r_t
+// r, k [T, *] of rk_dtype with row pitches r_ld, k_ld; v of v_dtype; wraw of w_dtype; out float32 [T, heads * dv].
+size_t exl3_linear_scan_scratch_bytes(int B, int T, int heads, int dk, int dv, int max_new);
+int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const void* k, int64_t k_ld, int rk_dtype, const void* v,
+                     int64_t v_ld, int v_dtype, const void* wraw, int64_t w_ld, int w_dtype, const void* w0,
+                     const void* u, int wu_dtype, const float* decay, float* state, const int* slot_ids,
+                     const int* row_start, float* out, int B, int T, int heads, int dk, int dv, int max_new,
+                     float* scratch, size_t scratch_bytes, cudaStream_t stream);
+// out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w[h, :] (w null: 1) * silu(gate[t, h, :]) (gate null: 1)
+int exl3_head_norm_gate(const float* o, const void* w, int w_dtype, const void* gate, int gate_dtype, int64_t gate_ld,
+                        float eps, void* out, int out_dtype, int T, int heads, int dv, cudaStream_t stream);
+// out[t] = coef * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb), float32 out
+int exl3_normed_sum2(const void* a, const void* b, int ab_dtype, const void* wa, const void* wb, int w_dtype, float eps,
+                     float coef, float* out, int T, int H, cudaStream_t stream);
+// kind 0: z/2 (1 + erf(z / sqrt 2)); 1: z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2: tanh(z)
+int exl3_activation(const void* z, int z_dtype, void* out, int out_dtype, int64_t n, int kind, cudaStream_t stream);
+
 // Attention over latent rows on the tensor cores (bfloat16; see attention_latent.cu).  q [T * H, dk] and out
 // [T * H, dv] hold the rows of each sequence's tokens of this step head by head; the pool holds one row of dk
 // features per key, page = 64 keys, whose first dv features are the values.  Batch row b has the tokens

@@ -24,6 +24,12 @@
 // pool holds hd key features (kv_row >= hd elements apart); a row of the value pool holds hdv <= hd value features
 // with the same row pitch.  Ordinary attention has hdv = hd = kv_row and two pools; an attention whose values are
 // the leading features of its keys (a latent shared by all heads) passes the key pool twice with hdv < hd.
+// The general entry point (exl3_attn_tokens_ex) gives the value pool a row pitch of its own (v_row), so that values
+// may also be wider than keys, and takes two more options:
+//   chunk > 0: a query at position p sees only the keys from floor(p / chunk) * chunk on (blocks of positions
+//              counted from the start of the sequence), on top of the causal bound and the window;
+//   sink:      one is added to the softmax's denominator, as if there were one more key with score 0 and a value
+//              of zero: p_j = exp(s_j) / (1 + sum_j exp(s_j)).
 #include "api.h"
 #include "common.cuh"
 
@@ -52,6 +58,16 @@ template <> struct SoftmaxExp<__nv_bfloat16> {
   }
 };
 
+// The last step of a row with a sink: the sink enters as one more key of score 0 (in either base) whose value is
+// zero.  Returns the factor for the accumulator; the denominator comes back in l.
+template <typename T>
+__device__ inline float sink_finish(float m, float& l) {
+  const float mn = fmaxf(m, 0.0f);
+  const float cs = SoftmaxExp<T>::exp(m - mn);
+  l = l * cs + SoftmaxExp<T>::exp(-mn);
+  return cs;
+}
+
 // merge (mo, lo, ao) into (m, l, a)
 template <typename T, int N>
 __device__ inline void merge_state(float& m, float& l, float (&a)[N], float mo, float lo, const float (&ao)[N]) {
@@ -70,9 +86,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict__ out,
                    const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
-                   const int* __restrict__ tok_seq, int nh, int nkv, int hd, int hdv, int kv_row, int page,
-                   int window, float scale, int split_keys, int max_splits, float* __restrict__ scratch,
-                   int* __restrict__ counters, int lpk) {
+                   const int* __restrict__ tok_seq, int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page,
+                   int window, int chunk, int sink, float scale, int split_keys, int max_splits,
+                   float* __restrict__ scratch, int* __restrict__ counters, int lpk) {
   constexpr int VEC = Elem<T>::vec;
   constexpr int NA = R * VEC;
   constexpr int U = R == 1 ? 4 : (R == 2 ? 2 : 1);  // key groups whose loads are issued together
@@ -87,7 +103,8 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
   const int grp = lane / lpk, li = lane - grp * lpk;
   const float scale_eff = scale * SoftmaxExp<T>::prescale;
   const int pos = __ldcg(tok_pos + t);
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (chunk > 0) lo = max(lo, pos / chunk * chunk);
   const int hi = pos + 1;
   // this block's chunk of keys
   int c_lo = lo, c_hi = hi;
@@ -130,6 +147,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
       for (int pi = first_page + warp; pi <= last_page; pi += ATT_WARPS) {
         const int pg = bt[pi];
         const int64_t page_base = ((int64_t)pg * nkv + g) * page * kv_row;
+        const int64_t page_base_v = ((int64_t)pg * nkv + g) * page * v_row;
         // U groups of keys at a time: all their loads are issued before the first is used
         for (int jj0 = grp; jj0 < page; jj0 += kpw * U) {   // same trip count for every lane
           uint4 rk[U][R], rv[U][R];
@@ -144,9 +162,9 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
               const int d = (r * lpk + li) * VEC;
               rk[u][r] = make_uint4(0, 0, 0, 0);
               rv[u][r] = make_uint4(0, 0, 0, 0);
-              if (valid[u] && d < hd) {
-                rk[u][r] = load_raw_cg(k_pool + page_base + (int64_t)jj * kv_row + d);
-                if (d < hdv) rv[u][r] = load_raw_cg(v_pool + page_base + (int64_t)jj * kv_row + d);
+              if (valid[u]) {
+                if (d < hd) rk[u][r] = load_raw_cg(k_pool + page_base + (int64_t)jj * kv_row + d);
+                if (d < hdv) rv[u][r] = load_raw_cg(v_pool + page_base_v + (int64_t)jj * v_row + d);
               }
             }
           }
@@ -237,6 +255,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
       }
       const int head = g * G + h0 + hh;
       if (max_splits <= 1) {
+        if (sink) aa *= sink_finish<T>(mm, ll);
         Elem<T>::store(out + ((int64_t)t * nh + head) * hdv + d, aa / ll);
       } else {
         float* sc = scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
@@ -273,11 +292,12 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
     __syncthreads();
     float ll = 0.0f;
     for (int s2 = 0; s2 < max_splits; ++s2) ll += sl[s2] * sw[s2];
+    const float fin = sink ? sink_finish<T>(mx, ll) : 1.0f;
     for (int d = threadIdx.x; d < hdv; d += blockDim.x) {
       float aa = 0.0f;
 #pragma unroll 4
       for (int s2 = 0; s2 < max_splits; ++s2) aa += __ldcg(base + (int64_t)s2 * rec + d) * sw[s2];
-      Elem<T>::store(out + ((int64_t)t * nh + head) * hdv + d, aa / ll);
+      Elem<T>::store(out + ((int64_t)t * nh + head) * hdv + d, aa * fin / ll);
     }
   }
   if (threadIdx.x == 0) counters[(int64_t)t * nkv + g] = 0;
@@ -288,7 +308,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
 // both sums in chunk order.  The records are read with independent loads.
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ scratch, T* __restrict__ out, int nh, int hd,
-                                    int max_splits) {
+                                    int max_splits, int sink) {
   extern __shared__ float sw[];                      // [max_splits] weights, then [max_splits] sums
   pdl_wait();
   pdl_trigger();
@@ -308,19 +328,20 @@ __global__ void attn_combine_kernel(const float* __restrict__ scratch, T* __rest
   __syncthreads();
   float ll = 0.0f;
   for (int s = 0; s < max_splits; ++s) ll += sl[s] * sw[s];
+  const float fin = sink ? sink_finish<T>(mx, ll) : 1.0f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float aa = 0.0f;
 #pragma unroll 4
     for (int s = 0; s < max_splits; ++s) aa += __ldcg(base + (int64_t)s * rec + d) * sw[s];
-    Elem<T>::store(out + ((int64_t)t * nh + head) * hd + d, aa / ll);
+    Elem<T>::store(out + ((int64_t)t * nh + head) * hd + d, aa * fin / ll);
   }
 }
 
 template <typename T, int GT, int R>
 static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const void* k_pool,
                          const void* v_pool, const int* block_table, int bt_stride, const int* tok_pos,
-                         const int* tok_seq, int T_, int nh, int nkv, int hd, int hdv, int kv_row, int page,
-                         int window, float scale, int split_keys, int max_splits, float* scratch, int lpk,
+                         const int* tok_seq, int T_, int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page,
+                         int window, int chunk, int sink, float scale, int split_keys, int max_splits, float* scratch, int lpk,
                          cudaStream_t stream) {
   const size_t smem = ((size_t)ATT_WARPS * GT * (hdv + 2) + 2 * (size_t)max_splits) * sizeof(float);
   if (smem > 48 * 1024) {
@@ -339,13 +360,13 @@ static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const v
   dim3 grid(T_, nkv, max_splits);
   launch_pdl(attn_tokens_kernel<T, GT, R>, grid, dim3(ATT_WARPS * 32), smem, stream,
              static_cast<const T*>(q), q_row_stride, static_cast<T*>(out), static_cast<const T*>(k_pool),
-             static_cast<const T*>(v_pool), block_table, bt_stride, tok_pos, tok_seq, nh, nkv, hd, hdv, kv_row, page,
-             window, scale, split_keys, max_splits, scratch, counters, lpk);
+             static_cast<const T*>(v_pool), block_table, bt_stride, tok_pos, tok_seq, nh, nkv, hd, hdv, kv_row, v_row, page,
+             window, chunk, sink, scale, split_keys, max_splits, scratch, counters, lpk);
   int rc = launch_status("attn_tokens");
   if (rc) return rc;
   if (max_splits > 1 && !fused_merge) {
     launch_pdl(attn_combine_kernel<T>, dim3(T_, nh), dim3(64), (size_t)2 * max_splits * sizeof(float), stream,
-               (const float*)scratch, static_cast<T*>(out), nh, hdv, max_splits);
+               (const float*)scratch, static_cast<T*>(out), nh, hdv, max_splits, sink);
     rc = launch_status("attn_combine");
   }
   return rc;
@@ -354,18 +375,18 @@ static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const v
 template <typename T>
 static int dispatch(const void* q, int64_t q_row_stride, void* out, const void* k_pool, const void* v_pool,
                     const int* block_table, int bt_stride, const int* tok_pos, const int* tok_seq, int T_,
-                    int nh, int nkv, int hd, int hdv, int kv_row, int page, int window, float scale, int split_keys,
-                    int max_splits, float* scratch, cudaStream_t stream) {
+                    int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page, int window, int chunk, int sink,
+                    float scale, int split_keys, int max_splits, float* scratch, cudaStream_t stream) {
   constexpr int VEC = Elem<T>::vec;
-  const int vecs = hd / VEC;                          // 16-byte pieces per head row
+  const int vecs = ceil_div(max(hd, hdv), VEC);       // 16-byte pieces of the wider of a key row and a value row
   int lpk = 1;
   while (lpk < vecs && lpk < 32) lpk <<= 1;
   const int R = ceil_div(vecs, lpk);
   const int G = nh / nkv;
 #define EXL3_ATT(GT, RR)                                                                                 \
   return launch_tokens<T, GT, RR>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos, \
-                                  tok_seq, T_, nh, nkv, hd, hdv, kv_row, page, window, scale, split_keys, \
-                                  max_splits, scratch, lpk, stream)
+                                  tok_seq, T_, nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale, \
+                                  split_keys, max_splits, scratch, lpk, stream)
   if (R == 1) {
     if (G == 1) EXL3_ATT(1, 1);
     if (G == 2) EXL3_ATT(2, 1);
@@ -400,18 +421,19 @@ extern "C" size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_
   return (size_t)ATT_COUNTER_SLOTS * sizeof(int) + (size_t)T * nh * max_splits * (hd + 2) * sizeof(float);
 }
 
-extern "C" int exl3_attn_tokens_kv(const void* q, int64_t q_row_stride, void* out, int dtype,
+extern "C" int exl3_attn_tokens_ex(const void* q, int64_t q_row_stride, void* out, int dtype,
                                    const void* k_pool, const void* v_pool, const int* block_table,
                                    int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
-                                   int hd, int hdv, int kv_row, int page, int window, float scale, int split_keys,
-                                   int max_splits, float* scratch, size_t scratch_bytes, cudaStream_t stream) {
+                                   int hd, int hdv, int kv_row, int v_row, int page, int window, int chunk, int sink,
+                                   float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
+                                   cudaStream_t stream) {
   if (T == 0) return 0;
-  if (T < 0 || nh < 1 || nkv < 1 || nh % nkv != 0 || hd < 16 || hd % 16 != 0 || hdv < 16 || hdv % 16 != 0 ||
-      hdv > hd || kv_row < hd || kv_row % 16 != 0 || page < 1 || window < 0 || max_splits < 1 || split_keys < 0 ||
-      (max_splits > 1 && split_keys == 0)) {
-    set_error("attn_tokens: bad sizes T=%d heads=%d kv_heads=%d head_dim=%d value_dim=%d row=%d (multiples of 16, "
-              "value_dim <= head_dim <= row) page=%d window=%d split_keys=%d max_splits=%d", T, nh, nkv, hd, hdv,
-              kv_row, page, window, split_keys, max_splits);
+  if (T < 0 || nh < 1 || nkv < 1 || nh % nkv != 0 || hd < 8 || hd % 8 != 0 || hdv < 8 || hdv % 8 != 0 ||
+      kv_row < hd || kv_row % 8 != 0 || v_row < hdv || v_row % 8 != 0 || page < 1 || window < 0 || chunk < 0 ||
+      max_splits < 1 || split_keys < 0 || (max_splits > 1 && split_keys == 0)) {
+    set_error("attn_tokens: bad sizes T=%d heads=%d kv_heads=%d head_dim=%d value_dim=%d rows=%d/%d (multiples of 8, "
+              "head_dim <= key row, value_dim <= value row) page=%d window=%d chunk=%d split_keys=%d max_splits=%d", T,
+              nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, split_keys, max_splits);
     return ERR_BAD_ARGUMENT;
   }
   if (split_keys % page != 0) {
@@ -431,13 +453,25 @@ extern "C" int exl3_attn_tokens_kv(const void* q, int64_t q_row_stride, void* ou
   }
   if (dtype == DT_F32)
     return dispatch<float>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq, T,
-                           nh, nkv, hd, hdv, kv_row, page, window, scale, split_keys, max_splits, scratch, stream);
+                           nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale, split_keys, max_splits,
+                           scratch, stream);
   if (dtype == DT_BF16)
     return dispatch<__nv_bfloat16>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos,
-                                   tok_seq, T, nh, nkv, hd, hdv, kv_row, page, window, scale, split_keys,
-                                   max_splits, scratch, stream);
+                                   tok_seq, T, nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale,
+                                   split_keys, max_splits, scratch, stream);
   set_error("attn_tokens: unsupported element type %d", dtype);
   return ERR_UNSUPPORTED;
+}
+
+extern "C" int exl3_attn_tokens_kv(const void* q, int64_t q_row_stride, void* out, int dtype,
+                                   const void* k_pool, const void* v_pool, const int* block_table,
+                                   int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
+                                   int hd, int hdv, int kv_row, int page, int window, float scale, int split_keys,
+                                   int max_splits, float* scratch, size_t scratch_bytes, cudaStream_t stream) {
+  if (hdv > hd) { set_error("attn_tokens_kv: value_dim %d above head_dim %d", hdv, hd); return ERR_BAD_ARGUMENT; }
+  return exl3_attn_tokens_ex(q, q_row_stride, out, dtype, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq, T,
+                             nh, nkv, hd, hdv, kv_row, kv_row, page, window, 0, 0, scale, split_keys, max_splits,
+                             scratch, scratch_bytes, stream);
 }
 
 extern "C" int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, int dtype,
@@ -445,7 +479,7 @@ extern "C" int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, 
                                 int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
                                 int hd, int page, int window, float scale, int split_keys, int max_splits,
                                 float* scratch, size_t scratch_bytes, cudaStream_t stream) {
-  return exl3_attn_tokens_kv(q, q_row_stride, out, dtype, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq, T,
-                             nh, nkv, hd, hd, hd, page, window, scale, split_keys, max_splits, scratch, scratch_bytes,
-                             stream);
+  return exl3_attn_tokens_ex(q, q_row_stride, out, dtype, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq, T,
+                             nh, nkv, hd, hd, hd, hd, page, window, 0, 0, scale, split_keys, max_splits, scratch,
+                             scratch_bytes, stream);
 }

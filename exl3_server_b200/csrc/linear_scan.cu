@@ -1,0 +1,326 @@
+// Linear recurrences with a matrix state per head, and what stands around them.
+//
+// State S [dk, dv] per (sequence, head), float32, kept in the cache's per-sequence state between steps.
+//
+//   mode 0, a decay per token and key channel and a bonus for the current token:
+//       o_t = S^T r_t + (sum_i r_ti u_i k_ti) v_t
+//       S  <- diag(w_t) S + k_t v_t^T,        w_t = exp(-exp(wraw_t + w0))
+//   mode 1, one decay per head (retention):
+//       S  <- decay_h S + k_t v_t^T
+//       o_t = S^T r_t
+//
+// A block owns one (row of the batch, head): thread j keeps column j of S in shared memory and walks the row's tokens
+// in order; r, k and the decays of eight tokens at a time are staged in shared memory.  The state is read from and
+// written back to the row's slot, so a sequence cut into steps in any way walks the same chain of sums.
+//
+// Rows that bring many tokens are cut into chunks of LS_CHUNK tokens that run side by side, as the element-wise
+// recurrence of recurrent.cu does: over a chunk S_out = diag(A) S_in + B with A the product of the chunk's decays
+// and B the chunk's own scan from zero.  A first launch leaves (A, B) per chunk, a second folds the (A, B) of the
+// chunks before its own, in order, into its start and walks its chunk.  That changes roundings only.  The row's last
+// chunk leaves the new state in the slot while the others may still be starting, so the first launch also copies the
+// state of every row that has more than one chunk into the scratch, and the second launch starts from that copy.
+//
+// Everything but the element types of r, k, v (a projection's output) is float32.
+#include "api.h"
+#include "common.cuh"
+
+namespace exl3 {
+
+__device__ inline float ls_load(const void* p, int dtype, int64_t i) {
+  return dtype == DT_F32 ? static_cast<const float*>(p)[i]
+                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ inline float ls_load_act(const void* p, int dtype, int64_t i) {
+  return dtype == DT_F32 ? __ldcg(static_cast<const float*>(p) + i)
+                         : __bfloat162float(__ldcg(static_cast<const __nv_bfloat16*>(p) + i));
+}
+__device__ inline void ls_store(void* p, int dtype, int64_t i, float v) {
+  if (dtype == DT_F32) static_cast<float*>(p)[i] = v;
+  else static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+// ---- token shift ---------------------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256)
+token_shift_kernel(const void* h, int h_dtype, const void* __restrict__ mu, int mu_dtype, int n_mix, float* prev,
+                   const int* __restrict__ tok_seq, const int* __restrict__ row_start,
+                   const int* __restrict__ slot_ids, void* out, int out_dtype, int T, int H) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int b = __ldcg(tok_seq + t);
+  const int first = __ldcg(row_start + b), end = __ldcg(row_start + b + 1);
+  float* st = prev + (int64_t)__ldcg(slot_ids + b) * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    const float x = ls_load_act(h, h_dtype, (int64_t)t * H + c);
+    float before;
+    if (t == first) {
+      // the same thread reads the entry and then leaves the row's last h of this step in it
+      before = __ldcg(st + c);
+      st[c] = ls_load_act(h, h_dtype, (int64_t)(end - 1) * H + c);
+    } else {
+      before = ls_load_act(h, h_dtype, (int64_t)(t - 1) * H + c);
+    }
+    const float d = before - x;
+    for (int s = 0; s < n_mix; ++s)
+      ls_store(out, out_dtype, ((int64_t)s * T + t) * H + c, fmaf(d, ls_load(mu, mu_dtype, (int64_t)s * H + c), x));
+  }
+}
+
+// ---- the scan ------------------------------------------------------------------------------------------------------
+
+constexpr int LS_STAGE = 8;                      // tokens staged in shared memory at a time
+constexpr int LS_CHUNK = 64;                     // tokens of a chunk when a row's tokens run side by side
+
+struct ScanArgs {
+  const void* r; int64_t r_ld; const void* k; int64_t k_ld; int rk_dtype;
+  const void* v; int64_t v_ld; int v_dtype;
+  const void* wraw; int64_t w_ld; int w_dtype;
+  const void* w0; const void* u; int wu_dtype;
+  const float* decay;
+  float* state; const int* slot_ids; const int* row_start;
+  float* out; float* ab; float* snap;
+  int heads, dk, dv, places;
+};
+
+// Chunk j of batch row b has a place of its own among floor(T / LS_CHUNK) + B + 1 places.
+__device__ inline int ls_place(int t0, int b, int j) { return t0 / LS_CHUNK + b + j; }
+
+// phase 0: a row's tokens of the step, from its state, state written back.
+// phase 1: a chunk from zero, (A, B) to scratch (no output; the row's last chunk does nothing).
+// phase 2: the chunks before folded into the state, then the chunk; the row's last chunk writes the state.
+template <int MODE>
+__global__ void linear_scan_kernel(ScanArgs a, int phase) {
+  extern __shared__ float ls_sm[];
+  const int dk = a.dk, dv = a.dv;
+  float* S = ls_sm;                              // [dk][dv]
+  float* sr = S + dk * dv;                       // [LS_STAGE][dk]
+  float* sk = sr + LS_STAGE * dk;                // [LS_STAGE][dk]
+  float* sw = sk + LS_STAGE * dk;                // [LS_STAGE][dk] decays (mode 0)
+  float* sb = sw + LS_STAGE * dk;                // [LS_STAGE] bonus factors (mode 0)
+  float* sA = sb + LS_STAGE;                     // [dk] product of decays (phase 1)
+  pdl_wait();
+  pdl_trigger();
+  const int hd = blockIdx.x, c = blockIdx.y, b = blockIdx.z;
+  const int t0 = __ldcg(a.row_start + b), t1 = __ldcg(a.row_start + b + 1);
+  int lo = t0, hi = t1;
+  if (phase == 1) {
+    lo = t0 + c * LS_CHUNK;
+    hi = lo + LS_CHUNK;
+    if (hi >= t1) return;                        // the row's last chunk has nobody after it
+  } else if (phase == 2) {
+    lo = t0 + c * LS_CHUNK;
+    hi = min(lo + LS_CHUNK, t1);
+    if (lo >= t1) return;
+  }
+  const int j = threadIdx.x;
+  const bool col = j < dv;
+  float* st = a.state + ((int64_t)__ldcg(a.slot_ids + b) * a.heads + hd) * dk * dv;
+  const int64_t rec = (int64_t)dk + (int64_t)dk * dv;      // floats of one (place, head): A then B
+  float* snap = a.snap + ((int64_t)b * a.heads + hd) * dk * dv;
+  if (phase == 1) {
+    if (col) for (int i = 0; i < dk; ++i) S[i * dv + j] = 0.0f;
+    for (int i = j; i < dk; i += blockDim.x) sA[i] = 1.0f;
+    if (c == 0 && col) for (int i = 0; i < dk; ++i) snap[i * dv + j] = __ldcg(st + i * dv + j);
+  } else {
+    // a row of several chunks starts from the copy that the first launch took
+    const float* from = (phase == 2 && t1 - t0 > LS_CHUNK) ? snap : st;
+    if (col) for (int i = 0; i < dk; ++i) S[i * dv + j] = __ldcg(from + i * dv + j);
+    if (phase == 2 && col) {
+      for (int p = 0; p < c; ++p) {              // the chunks before this one, in order
+        const float* ab = a.ab + ((int64_t)ls_place(t0, b, p) * a.heads + hd) * rec;
+        for (int i = 0; i < dk; ++i) S[i * dv + j] = fmaf(__ldcg(ab + i), S[i * dv + j], __ldcg(ab + dk + i * dv + j));
+      }
+    }
+  }
+  const float gamma = MODE == 1 ? a.decay[hd] : 0.0f;
+  for (int s0 = lo; s0 < hi; s0 += LS_STAGE) {
+    const int n = min(LS_STAGE, hi - s0);
+    __syncthreads();                             // the stage before has been used
+    for (int idx = threadIdx.x; idx < n * dk; idx += blockDim.x) {
+      const int tt = idx / dk, i = idx - tt * dk;
+      const int64_t t = s0 + tt;
+      sr[idx] = ls_load_act(a.r, a.rk_dtype, t * a.r_ld + (int64_t)hd * dk + i);
+      sk[idx] = ls_load_act(a.k, a.rk_dtype, t * a.k_ld + (int64_t)hd * dk + i);
+      if (MODE == 0) {
+        const float z = ls_load_act(a.wraw, a.w_dtype, t * a.w_ld + (int64_t)hd * dk + i) +
+                        ls_load(a.w0, a.wu_dtype, (int64_t)hd * dk + i);
+        sw[idx] = expf(-expf(z));
+      }
+    }
+    __syncthreads();
+    if (MODE == 0) {
+      // the bonus factor sum_i r_i u_i k_i of each staged token, a warp a token
+      const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+      for (int tt = warp; tt < n; tt += nw) {
+        float acc = 0.0f;
+        for (int i = lane; i < dk; i += 32)
+          acc = fmaf(sr[tt * dk + i] * ls_load(a.u, a.wu_dtype, (int64_t)hd * dk + i), sk[tt * dk + i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) sb[tt] = acc;
+      }
+      if (phase == 1)
+        for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+          float p = sA[i];
+          for (int tt = 0; tt < n; ++tt) p *= sw[tt * dk + i];
+          sA[i] = p;
+        }
+      __syncthreads();
+    } else if (phase == 1) {
+      for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+        float p = sA[i];
+        for (int tt = 0; tt < n; ++tt) p *= gamma;
+        sA[i] = p;
+      }
+    }
+    if (col) {
+      for (int tt = 0; tt < n; ++tt) {
+        const int64_t t = s0 + tt;
+        const float vj = ls_load_act(a.v, a.v_dtype, t * a.v_ld + (int64_t)hd * dv + j);
+        const float* rr = sr + tt * dk;
+        const float* kk = sk + tt * dk;
+        float acc = 0.0f;
+        if (MODE == 0) {
+          const float* ww = sw + tt * dk;
+#pragma unroll 4
+          for (int i = 0; i < dk; ++i) {
+            const float s = S[i * dv + j];
+            acc = fmaf(rr[i], s, acc);
+            S[i * dv + j] = fmaf(ww[i], s, kk[i] * vj);
+          }
+          acc = fmaf(sb[tt], vj, acc);
+        } else {
+#pragma unroll 4
+          for (int i = 0; i < dk; ++i) {
+            const float s = fmaf(gamma, S[i * dv + j], kk[i] * vj);
+            S[i * dv + j] = s;
+            acc = fmaf(rr[i], s, acc);
+          }
+        }
+        if (phase != 1) a.out[t * ((int64_t)a.heads * dv) + (int64_t)hd * dv + j] = acc;
+      }
+    }
+  }
+  if (phase == 1) {
+    __syncthreads();
+    float* ab = a.ab + ((int64_t)ls_place(t0, b, c) * a.heads + hd) * rec;
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) ab[i] = sA[i];
+    if (col) for (int i = 0; i < dk; ++i) ab[dk + i * dv + j] = S[i * dv + j];
+  } else if (hi == t1 && col) {
+    for (int i = 0; i < dk; ++i) st[i * dv + j] = S[i * dv + j];
+  }
+}
+
+// ---- per-head norm and gate ------------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, const void* gate, int gate_dtype,
+                      int64_t gate_ld, float eps, void* out, int out_dtype, int n_items, int heads, int dv) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);       // (token, head)
+  if (item >= n_items) return;
+  const int t = item / heads, hd = item - t * heads;
+  const float* src = o + (int64_t)item * dv;
+  float ss = 0.0f;
+  for (int e = lane; e < dv; e += 32) {
+    const float x = __ldcg(src + e);
+    ss += x * x;
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+  for (int e = lane; e < dv; e += 32) {
+    float x = __ldcg(src + e) * inv;
+    if (w) x *= ls_load(w, w_dtype, (int64_t)hd * dv + e);
+    if (gate) {
+      const float g = ls_load_act(gate, gate_dtype, (int64_t)t * gate_ld + (int64_t)hd * dv + e);
+      x *= g / (1.0f + expf(-g));
+    }
+    ls_store(out, out_dtype, (int64_t)item * dv + e, x);
+  }
+}
+
+}  // namespace exl3
+
+using namespace exl3;
+
+static bool ls_chunked(int max_new) { return max_new > 2 * LS_CHUNK; }
+
+extern "C" size_t exl3_linear_scan_scratch_bytes(int B, int T, int heads, int dk, int dv, int max_new) {
+  if (!ls_chunked(max_new)) return 0;
+  return ((size_t)(T / LS_CHUNK + B + 1) * heads * ((size_t)dk + (size_t)dk * dv) + (size_t)B * heads * dk * dv) *
+         sizeof(float);
+}
+
+extern "C" int exl3_token_shift(const void* h, int h_dtype, const void* mu, int mu_dtype, int n_mix, float* prev,
+                                const int* tok_seq, const int* row_start, const int* slot_ids, void* out,
+                                int out_dtype, int T, int H, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || H < 1 || n_mix < 1 || prev == nullptr) {
+    set_error("token_shift: bad sizes T=%d H=%d mixes=%d", T, H, n_mix);
+    return ERR_BAD_ARGUMENT;
+  }
+  launch_pdl(token_shift_kernel, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream, h, h_dtype, mu, mu_dtype, n_mix,
+             prev, tok_seq, row_start, slot_ids, out, out_dtype, T, H);
+  return launch_status("token_shift");
+}
+
+extern "C" int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const void* k, int64_t k_ld, int rk_dtype,
+                                const void* v, int64_t v_ld, int v_dtype, const void* wraw, int64_t w_ld, int w_dtype,
+                                const void* w0, const void* u, int wu_dtype, const float* decay, float* state,
+                                const int* slot_ids, const int* row_start, float* out, int B, int T, int heads, int dk,
+                                int dv, int max_new, float* scratch, size_t scratch_bytes, cudaStream_t stream) {
+  if (B == 0 || T == 0) return 0;
+  if (B < 0 || T < 0 || heads < 1 || dk < 1 || dv < 1 || dv > 1024 || B > 65535 || mode < 0 || mode > 1 ||
+      (mode == 0 && (wraw == nullptr || w0 == nullptr || u == nullptr)) || (mode == 1 && decay == nullptr)) {
+    set_error("linear_scan: bad arguments mode=%d rows=%d tokens=%d heads=%d dk=%d dv=%d", mode, B, T, heads, dk, dv);
+    return ERR_BAD_ARGUMENT;
+  }
+  const size_t smem = ((size_t)dk * dv + 3 * (size_t)LS_STAGE * dk + LS_STAGE + dk) * sizeof(float);
+  if (smem > 200 * 1024) {
+    set_error("linear_scan: a state of %d x %d per head does not fit shared memory", dk, dv);
+    return ERR_UNSUPPORTED;
+  }
+  auto kernel = mode == 0 ? linear_scan_kernel<0> : linear_scan_kernel<1>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      set_error("linear_scan: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+      return (int)e;
+    }
+  }
+  ScanArgs a;
+  a.r = r; a.r_ld = r_ld; a.k = k; a.k_ld = k_ld; a.rk_dtype = rk_dtype; a.v = v; a.v_ld = v_ld; a.v_dtype = v_dtype;
+  a.wraw = wraw; a.w_ld = w_ld; a.w_dtype = w_dtype; a.w0 = w0; a.u = u; a.wu_dtype = wu_dtype; a.decay = decay;
+  a.state = state; a.slot_ids = slot_ids; a.row_start = row_start; a.out = out; a.ab = scratch;
+  a.heads = heads; a.dk = dk; a.dv = dv; a.places = T / LS_CHUNK + B + 1;
+  a.snap = scratch ? scratch + (size_t)a.places * heads * ((size_t)dk + (size_t)dk * dv) : nullptr;
+  const int threads = (dv + 31) / 32 * 32;
+  if (ls_chunked(max_new)) {
+    const int chunks = ceil_div(max_new, LS_CHUNK);
+    if (scratch == nullptr || exl3_linear_scan_scratch_bytes(B, T, heads, dk, dv, max_new) > scratch_bytes ||
+        chunks > 65535) {
+      set_error("linear_scan: scratch of %zu bytes is too small for %d tokens", scratch_bytes, T);
+      return ERR_SCRATCH;
+    }
+    launch_pdl(kernel, dim3(heads, chunks, B), dim3(threads), smem, stream, a, 1);
+    int rc = launch_status("linear_scan (chunks)");
+    if (rc) return rc;
+    launch_pdl(kernel, dim3(heads, chunks, B), dim3(threads), smem, stream, a, 2);
+    return launch_status("linear_scan (fold)");
+  }
+  launch_pdl(kernel, dim3(heads, 1, B), dim3(threads), smem, stream, a, 0);
+  return launch_status("linear_scan");
+}
+
+extern "C" int exl3_head_norm_gate(const float* o, const void* w, int w_dtype, const void* gate, int gate_dtype,
+                                   int64_t gate_ld, float eps, void* out, int out_dtype, int T, int heads, int dv,
+                                   cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || heads < 1 || dv < 1) { set_error("head_norm_gate: bad sizes"); return ERR_BAD_ARGUMENT; }
+  const int items = T * heads;
+  launch_pdl(head_norm_gate_kernel, dim3(ceil_div(items, 4)), dim3(128), 0, stream, o, w, w_dtype, gate, gate_dtype,
+             gate_ld, eps, out, out_dtype, items, heads, dv);
+  return launch_status("head_norm_gate");
+}

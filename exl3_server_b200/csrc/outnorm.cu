@@ -180,9 +180,98 @@ static void norm_add_vec(float* h, const void* y, const void* w, float eps, void
                static_cast<const TY*>(y), static_cast<const TW*>(w), eps, static_cast<__nv_bfloat16*>(x), H);
 }
 
+// Two sublayer outputs side by side, each normed over the row with its own weight, then averaged:
+//   out[t] = coef * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb), float32.
+__global__ void __launch_bounds__(NA_THREADS)
+normed_sum2_kernel(const void* a, const void* b, int ab_dtype, const void* __restrict__ wa, const void* __restrict__ wb,
+                   int w_dtype, float eps, float coef, float* out, int H) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int64_t base = (int64_t)blockIdx.x * H;
+  float sa = 0.0f, sb = 0.0f;
+  for (int c = threadIdx.x; c < H; c += NA_THREADS) {
+    const float x = on_load_act(a, ab_dtype, base + c), y = on_load_act(b, ab_dtype, base + c);
+    sa += x * x;
+    sb += y * y;
+  }
+  sa = block_sum(sa, red);
+  sb = block_sum(sb, red);
+  const float ia = 1.0f / sqrtf(sa / (float)H + eps), ib = 1.0f / sqrtf(sb / (float)H + eps);
+  for (int c = threadIdx.x; c < H; c += NA_THREADS) {
+    const float x = on_load_act(a, ab_dtype, base + c) * ia * on_load_any(wa, w_dtype, c);
+    const float y = on_load_act(b, ab_dtype, base + c) * ib * on_load_any(wb, w_dtype, c);
+    out[base + c] = coef * (x + y);
+  }
+}
+
+// Element-wise activations, float32 inside: GELU exact (erf, kind 0) or by the tanh formula (1), and tanh (2).
+__device__ inline float act_apply(float v, int kind) {
+  if (kind == 0) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+  if (kind == 1) return 0.5f * v * (1.0f + tanhf(0.79788456080286536f * (v + 0.044715f * v * v * v)));
+  return tanhf(v);
+}
+
+__global__ void gelu_kernel(const void* z, int z_dtype, void* out, int out_dtype, int64_t n, int kind) {
+  pdl_wait();
+  pdl_trigger();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = on_load_act(z, z_dtype, i);
+    on_store_any(out, out_dtype, i, act_apply(v, kind));
+  }
+}
+
+template <typename TI, typename TO>
+__global__ void gelu_vec_kernel(const TI* z, TO* out, int64_t n8, int kind) {
+  pdl_wait();
+  pdl_trigger();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    float v[8];
+    on_load8(z + i * 8, v, true);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = act_apply(v[e], kind);
+    on_store8(out + i * 8, v);
+  }
+}
+
 }  // namespace exl3
 
 using namespace exl3;
+
+extern "C" int exl3_normed_sum2(const void* a, const void* b, int ab_dtype, const void* wa, const void* wb, int w_dtype,
+                                float eps, float coef, float* out, int T, int H, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || H < 1 || a == nullptr || b == nullptr || wa == nullptr || wb == nullptr) {
+    set_error("normed_sum2: bad arguments T=%d H=%d", T, H);
+    return ERR_BAD_ARGUMENT;
+  }
+  launch_pdl(normed_sum2_kernel, dim3(T), dim3(NA_THREADS), 0, stream, a, b, ab_dtype, wa, wb, w_dtype, eps, coef, out, H);
+  return launch_status("normed_sum2");
+}
+
+extern "C" int exl3_activation(const void* z, int z_dtype, void* out, int out_dtype, int64_t n, int kind, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (n < 0 || kind < 0 || kind > 2) { set_error("activation: bad arguments"); return ERR_BAD_ARGUMENT; }
+  if (n % 8 == 0 && aligned16(z) && aligned16(out)) {
+    const int64_t n8 = n / 8;
+    int64_t blocks = (n8 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    const dim3 g((unsigned)blocks), t(256);
+    if (z_dtype == DT_F32 && out_dtype == DT_BF16)
+      launch_pdl(gelu_vec_kernel<float, __nv_bfloat16>, g, t, 0, stream, static_cast<const float*>(z), static_cast<__nv_bfloat16*>(out), n8, kind);
+    else if (z_dtype == DT_BF16 && out_dtype == DT_BF16)
+      launch_pdl(gelu_vec_kernel<__nv_bfloat16, __nv_bfloat16>, g, t, 0, stream, static_cast<const __nv_bfloat16*>(z), static_cast<__nv_bfloat16*>(out), n8, kind);
+    else if (z_dtype == DT_F32 && out_dtype == DT_F32)
+      launch_pdl(gelu_vec_kernel<float, float>, g, t, 0, stream, static_cast<const float*>(z), static_cast<float*>(out), n8, kind);
+    else
+      launch_pdl(gelu_vec_kernel<__nv_bfloat16, float>, g, t, 0, stream, static_cast<const __nv_bfloat16*>(z), static_cast<float*>(out), n8, kind);
+    return launch_status("activation");
+  }
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  launch_pdl(gelu_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, z, z_dtype, out, out_dtype, n, kind);
+  return launch_status("activation");
+}
 
 extern "C" int exl3_norm_add(float* h, const void* y, int y_dtype, const void* w, int w_dtype, float eps, void* x,
                              int x_dtype, int T, int H, cudaStream_t stream) {

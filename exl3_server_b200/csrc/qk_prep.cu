@@ -1,0 +1,175 @@
+// What lies between an attention's joint input projection and the attention itself, in one kernel:
+//
+//   queries and keys, head by head: x <- x / sqrt(mean(x^2) + eps) (* w)         (norm 1 / 2; 0: as they are)
+//   rotary encoding of the first `rot` features at the token's position p, angle a_i = p f_i:
+//       layout 0 pairs feature i with i + rot / 2, layout 1 feature 2i with 2i + 1;
+//       (u, v) <- (u cos a - v sin a, v cos a + u sin a), sines and cosines times mscale
+//   keys times k_mul
+//   values: v <- (1 - lambda) v + lambda v_src   when a mixing weight is given (v_src: another layer's values of
+//       the same token)
+//   queries to q_out; keys and values to the token's place in the paged cache, or keys to k_out when there is no
+//   cache (mixers that keep a state instead).
+//
+// Rows of q_out, k_out and the cache hold hd_pad >= hd (hdv_pad >= hdv) features; the features beyond a head's own
+// are written as zeros, so that kernels which read rows in 16-byte pieces take any even head size.  All arithmetic
+// is float32; inputs and outputs have their own element types.
+#include "api.h"
+#include "common.cuh"
+
+namespace exl3 {
+
+__device__ inline float qp_load(const void* p, int dtype, int64_t i) {
+  return dtype == DT_F32 ? static_cast<const float*>(p)[i]
+                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ inline float qp_load_act(const void* p, int dtype, int64_t i) {
+  return dtype == DT_F32 ? __ldcg(static_cast<const float*>(p) + i)
+                         : __bfloat162float(__ldcg(static_cast<const __nv_bfloat16*>(p) + i));
+}
+__device__ inline void qp_store(void* p, int dtype, int64_t i, float v) {
+  if (dtype == DT_F32) static_cast<float*>(p)[i] = v;
+  else static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+constexpr int QP_WARPS = 4;
+
+struct QkPrepArgs {
+  const void* x; int x_dtype; int64_t ld; int q_off, k_off, v_off;
+  int nh, nkv, hd, hdv, hd_pad, hdv_pad;
+  int norm; const void* q_w; const void* k_w; int w_dtype; float eps;
+  int rot, layout; const float* f_hi; const float* f_lo; float mscale, k_mul;
+  const void* lambda; int lambda_dtype; const void* v_src; int v_src_dtype; int64_t v_src_ld;
+  const int* tok_pos; const int* tok_seq; const int* block_table; int bt_stride, page;
+  void* q_out; int q_out_dtype; void* k_out; int k_out_dtype; void* k_pool; void* v_pool; int pool_dtype;
+};
+
+__global__ void __launch_bounds__(QP_WARPS * 32) qk_prep_kernel(QkPrepArgs a) {
+  extern __shared__ float qp_sm[];                    // [QP_WARPS][max(hd, hdv)]
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int wide = max(a.hd, a.hdv);
+  float* sm = qp_sm + warp * wide;
+  const int pos = __ldcg(a.tok_pos + t);
+  int pg = -1;
+  if (a.k_pool != nullptr)
+    pg = __ldcg(a.block_table + (int64_t)__ldcg(a.tok_seq + t) * a.bt_stride + pos / a.page);
+  const int in_page = a.k_pool != nullptr ? pos % a.page : 0;
+  const int jobs = a.nh + a.nkv + (a.v_off >= 0 ? a.nkv : 0);
+  const float fpos = (float)pos;
+  for (int job = warp; job < jobs; job += QP_WARPS) {
+    const bool is_q = job < a.nh;
+    const bool is_k = !is_q && job < a.nh + a.nkv;
+    const int head = is_q ? job : (is_k ? job - a.nh : job - a.nh - a.nkv);
+    if (!is_q && !is_k) {
+      // a value head
+      const int64_t src = (int64_t)t * a.ld + a.v_off + (int64_t)head * a.hdv;
+      float lam = 0.0f;
+      if (a.lambda != nullptr) lam = qp_load(a.lambda, a.lambda_dtype, 0);
+      if (a.v_pool == nullptr || pg < 0) continue;
+      const int64_t dst = (((int64_t)pg * a.nkv + head) * a.page + in_page) * a.hdv_pad;
+      for (int e = lane; e < a.hdv_pad; e += 32) {
+        float v = 0.0f;
+        if (e < a.hdv) {
+          v = qp_load_act(a.x, a.x_dtype, src + e);
+          if (a.lambda != nullptr) {
+            const float o = qp_load_act(a.v_src, a.v_src_dtype, (int64_t)t * a.v_src_ld + (int64_t)head * a.hdv + e);
+            v = (1.0f - lam) * v + lam * o;
+          }
+        }
+        qp_store(a.v_pool, a.pool_dtype, dst + e, v);
+      }
+      continue;
+    }
+    const int64_t src = (int64_t)t * a.ld + (is_q ? a.q_off : a.k_off) + (int64_t)head * a.hd;
+    float ss = 0.0f;
+    for (int e = lane; e < a.hd; e += 32) {
+      const float v = qp_load_act(a.x, a.x_dtype, src + e);
+      sm[e] = v;
+      ss += v * v;
+    }
+    float inv = 1.0f;
+    if (a.norm) {
+      ss = warp_sum(ss);
+      inv = 1.0f / sqrtf(ss / (float)a.hd + a.eps);
+    }
+    __syncwarp();
+    const void* w = a.norm == 2 ? (is_q ? a.q_w : a.k_w) : nullptr;
+    const float mul = is_k ? a.k_mul : 1.0f;
+    void* out;
+    int out_dtype;
+    int64_t dst;
+    if (is_q) {
+      out = a.q_out; out_dtype = a.q_out_dtype;
+      dst = ((int64_t)t * a.nh + head) * a.hd_pad;
+    } else if (a.k_pool != nullptr) {
+      if (pg < 0) { __syncwarp(); continue; }
+      out = a.k_pool; out_dtype = a.pool_dtype;
+      dst = (((int64_t)pg * a.nkv + head) * a.page + in_page) * a.hd_pad;
+    } else {
+      out = a.k_out; out_dtype = a.k_out_dtype;
+      dst = ((int64_t)t * a.nkv + head) * a.hd_pad;
+    }
+    const int half = a.rot >> 1;
+    for (int e = lane; e < a.hd_pad; e += 32) {
+      float v = 0.0f;
+      if (e < a.hd) {
+        v = sm[e] * inv * (w ? qp_load(w, a.w_dtype, e) : 1.0f);
+        if (e < a.rot) {
+          int i, pe;
+          bool second;
+          if (a.layout == 1) { i = e >> 1; second = e & 1; pe = e ^ 1; }
+          else { second = e >= half; i = second ? e - half : e; pe = second ? e - half : e + half; }
+          const float o = sm[pe] * inv * (w ? qp_load(w, a.w_dtype, pe) : 1.0f);
+          float sn, cs;
+          rope_sincos(fpos, a.f_hi[i], a.f_lo ? a.f_lo[i] : 0.0f, &sn, &cs);
+          sn *= a.mscale;
+          cs *= a.mscale;
+          v = second ? fmaf(v, cs, o * sn) : fmaf(v, cs, -o * sn);
+        }
+        v *= mul;
+      }
+      qp_store(out, out_dtype, dst + e, v);
+    }
+    __syncwarp();                                       // the warp's row of shared memory is free again
+  }
+}
+
+}  // namespace exl3
+
+using namespace exl3;
+
+extern "C" int exl3_qk_prep(const void* x, int x_dtype, int64_t ld, int q_off, int k_off, int v_off, int T, int nh,
+                            int nkv, int hd, int hdv, int hd_pad, int hdv_pad, int norm, const void* q_w,
+                            const void* k_w, int w_dtype, float eps, int rot, int layout, const float* inv_freq,
+                            const float* inv_freq_lo, float mscale, float k_mul, const void* mix_lambda,
+                            int lambda_dtype, const void* v_src, int v_src_dtype, int64_t v_src_ld, const int* tok_pos,
+                            const int* tok_seq, const int* block_table, int bt_stride, int page, void* q_out,
+                            int q_out_dtype, void* k_out, int k_out_dtype, void* k_pool, void* v_pool, int pool_dtype,
+                            cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || nh < 1 || nkv < 1 || hd < 1 || hd_pad < hd || (v_off >= 0 && (hdv < 1 || hdv_pad < hdv)) ||
+      norm < 0 || norm > 2 || rot < 0 || rot > hd || rot % 2 != 0 || layout < 0 || layout > 1 ||
+      (rot > 0 && inv_freq == nullptr) || (norm == 2 && (q_w == nullptr || k_w == nullptr)) || q_out == nullptr ||
+      (k_pool == nullptr && k_out == nullptr) || (k_pool != nullptr && (block_table == nullptr || page < 1)) ||
+      (v_off >= 0 && k_pool != nullptr && v_pool == nullptr) || (mix_lambda != nullptr && v_src == nullptr)) {
+    set_error("qk_prep: bad arguments T=%d heads=%d/%d head_dim=%d (%d) value_dim=%d (%d) norm=%d rot=%d layout=%d",
+              T, nh, nkv, hd, hd_pad, hdv, hdv_pad, norm, rot, layout);
+    return ERR_BAD_ARGUMENT;
+  }
+  QkPrepArgs a;
+  a.x = x; a.x_dtype = x_dtype; a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
+  a.nh = nh; a.nkv = nkv; a.hd = hd; a.hdv = v_off >= 0 ? hdv : 0; a.hd_pad = hd_pad; a.hdv_pad = hdv_pad;
+  a.norm = norm; a.q_w = q_w; a.k_w = k_w; a.w_dtype = w_dtype; a.eps = eps;
+  a.rot = rot; a.layout = layout; a.f_hi = inv_freq; a.f_lo = inv_freq_lo; a.mscale = mscale; a.k_mul = k_mul;
+  a.lambda = mix_lambda; a.lambda_dtype = lambda_dtype; a.v_src = v_src; a.v_src_dtype = v_src_dtype;
+  a.v_src_ld = v_src_ld;
+  a.tok_pos = tok_pos; a.tok_seq = tok_seq; a.block_table = block_table; a.bt_stride = bt_stride; a.page = page;
+  a.q_out = q_out; a.q_out_dtype = q_out_dtype; a.k_out = k_out; a.k_out_dtype = k_out_dtype;
+  a.k_pool = k_pool; a.v_pool = v_pool; a.pool_dtype = pool_dtype;
+  const size_t smem = (size_t)QP_WARPS * (hd > a.hdv ? hd : a.hdv) * sizeof(float);
+  if (smem > 48 * 1024) { set_error("qk_prep: heads of %d features are too wide", hd); return ERR_UNSUPPORTED; }
+  launch_pdl(qk_prep_kernel, dim3(T), dim3(QP_WARPS * 32), smem, stream, a);
+  return launch_status("qk_prep");
+}

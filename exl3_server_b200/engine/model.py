@@ -27,6 +27,12 @@ def plan_manifest(plan: ModelPlan) -> List[TensorSpec]:
     for layer in plan.layers:
         specs += mixer_class(layer.mixer.kind).tensor_specs(layer.mixer, layer.names["mixer"])
         specs += norm_class(layer.mixer_norm.kind).tensor_specs(layer.mixer_norm, layer.names["mixer_norm"])
+        if layer.mixer_out_norm is not None:
+            specs += norm_class(layer.mixer_out_norm.kind).tensor_specs(layer.mixer_out_norm,
+                                                                        layer.names["mixer_out_norm"])
+        if layer.feed_forward is not None and layer.feed_forward_out_norm is not None:
+            specs += norm_class(layer.feed_forward_out_norm.kind).tensor_specs(layer.feed_forward_out_norm,
+                                                                               layer.names["feed_forward_out_norm"])
         if layer.feed_forward is not None:
             specs += feed_forward_class(layer.feed_forward.kind).tensor_specs(layer.feed_forward,
                                                                              layer.names["feed_forward"])
@@ -55,7 +61,17 @@ class Model:
                                                                  layer.names["feed_forward"], ctx)
                 n2 = norm_class(layer.feed_forward_norm.kind)(layer.feed_forward_norm, tensors,
                                                               layer.names["feed_forward_norm"], ctx)
-            self.blocks.append(arrangement_class(layer.arrangement)(layer, mixer, ff, n1, n2))
+            if layer.mixer_out_norm is not None or layer.feed_forward_out_norm is not None:
+                outs = [None, None]
+                if layer.mixer_out_norm is not None:
+                    outs[0] = norm_class(layer.mixer_out_norm.kind)(layer.mixer_out_norm, tensors,
+                                                                    layer.names["mixer_out_norm"], ctx)
+                if ff is not None and layer.feed_forward_out_norm is not None:
+                    outs[1] = norm_class(layer.feed_forward_out_norm.kind)(layer.feed_forward_out_norm, tensors,
+                                                                           layer.names["feed_forward_out_norm"], ctx)
+                self.blocks.append(arrangement_class(layer.arrangement)(layer, mixer, ff, n1, n2, out_norms=tuple(outs)))
+            else:
+                self.blocks.append(arrangement_class(layer.arrangement)(layer, mixer, ff, n1, n2))
         self.final_norm = norm_class(plan.final_norm.kind)(plan.final_norm, tensors, plan.final_norm_name, ctx)
         self.head = head_class(plan.head.kind)(plan.head, tensors, self.embedding, ctx)
         self.vocab = plan.head.vocab
@@ -68,11 +84,21 @@ class Model:
         return out
 
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None) -> SequenceCache:
+        extra = {}
+        if getattr(self.embedding, "state_request", None) is not None:
+            req = self.embedding.state_request()
+            if req is not None:
+                extra["embedding"] = req
         return SequenceCache(self.cache_requests(), max_tokens, dtype=self.dtype, device=self.device,
-                             max_slots=max_slots)
+                             max_slots=max_slots, extra_states=extra)
 
     def forward(self, batch: StepBatch, cache: SequenceCache) -> Optional[torch.Tensor]:
-        stream = self.embedding.forward(batch.token_ids)
+        if getattr(self.embedding, "takes_batch", False):
+            # an embedding that looks beyond the token itself (the token before, positions) gets the step and its
+            # per-sequence state
+            stream = self.embedding.forward(batch.token_ids, batch, cache.state_of("embedding"))
+        else:
+            stream = self.embedding.forward(batch.token_ids)
         sched = self.plan.schedule
         for i, e in enumerate(sched):
             block = self.blocks[e.layer]

@@ -513,6 +513,192 @@ def attn_tokens_kv(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool
     return out
 
 
+def attn_tokens_ex(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor,
+                   v_pool: torch.Tensor, block_table: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
+                   T: int, heads: int, kv_heads: int, head_dim: int, value_dim: int, page: int, window: int,
+                   chunk: int, sink: bool, scale: float, split_keys: int, max_splits: int,
+                   scratch: Optional[torch.Tensor]) -> torch.Tensor:
+    """``attn_tokens`` in its general form: rows of the key pool hold ``head_dim`` features and rows of the value
+    pool ``value_dim`` (each pool's last dimension is its row pitch; multiples of 8; values may be wider than keys);
+    ``chunk`` > 0 also hides every key before ``floor(pos / chunk) * chunk``; ``sink`` adds one to the softmax's
+    denominator.  ``out`` is ``[T, heads, value_dim]`` and the scratch is sized with ``value_dim``."""
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelLibraryError("attn_tokens_ex: q, cache and out differ in element type")
+    nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
+    _check(library().exl3_attn_tokens_ex(
+        _ptr(q), _c_int64(q_row_stride), _ptr(out), _c_int(dtype_code(q.dtype)), _ptr(k_pool), _ptr(v_pool),
+        _ptr(block_table), _c_int(block_table.stride(0)), _ptr(tok_pos), _ptr(tok_seq), _c_int(T),
+        _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(value_dim), _c_int(k_pool.shape[-1]),
+        _c_int(v_pool.shape[-1]), _c_int(page), _c_int(window), _c_int(chunk), _c_int(1 if sink else 0),
+        _c_float(scale), _c_int(split_keys), _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), _stream()),
+        "attn_tokens_ex")
+    return out
+
+
+def embed_hashed(ids: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor, row_start: torch.Tensor,
+                 slot_ids: torch.Tensor, table: torch.Tensor, extra: torch.Tensor, buckets: int, mul_prev: int,
+                 mul_cur: int, last_token: torch.Tensor) -> torch.Tensor:
+    """``table[id] + extra[(prev * mul_prev + id * mul_cur) mod buckets]`` as float32 rows (``extra[buckets]`` at
+    position 0); ``last_token`` (int32 per slot) gives the token before a row's first one and is left holding the
+    row's last one (see hashed_embed.cu)."""
+    T = ids.numel()
+    V, H = table.shape
+    _contig(table, "table")
+    _contig(extra, "extra")
+    if ids.dtype != torch.int32 or last_token.dtype != torch.int32:
+        raise KernelLibraryError("embed_hashed: ids and last_token must be int32")
+    if extra.dtype != table.dtype or tuple(extra.shape) != (buckets + 1, H):
+        raise KernelLibraryError(f"embed_hashed: the second table must be {(buckets + 1, H)} in the first one's type")
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _check(library().exl3_embed_hashed(
+        _ptr(ids), _ptr(tok_pos), _ptr(tok_seq), _ptr(row_start), _ptr(slot_ids), _ptr(table), _ptr(extra),
+        _c_int(dtype_code(table.dtype)), _c_int(buckets), ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur),
+        _ptr(last_token), _ptr(out), _c_int(T), _c_int(H), _c_int(V), _stream()), "embed_hashed")
+    return out
+
+
+def qk_prep(x: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, kv_heads: int, head_dim: int,
+            value_dim: int, head_pad: int, value_pad: int, norm: int, q_w: Optional[torch.Tensor],
+            k_w: Optional[torch.Tensor], eps: float, rot: int, layout: int, inv_freq: Optional[torch.Tensor],
+            mscale: float, k_mul: float, mix: Optional[tuple], tok_pos: torch.Tensor, tok_seq: torch.Tensor,
+            block_table: Optional[torch.Tensor], page: int, q_dtype: torch.dtype,
+            k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+            k_dtype: Optional[torch.dtype] = None):
+    """Norm, rotation, value mixing and the cache write between an attention's joint projection ``x [T, ld]`` and
+    the attention (see qk_prep.cu).  ``mix``: ``(lambda tensor, v_src [T, *] view)`` or None.  Returns ``(q, k)``:
+    the queries ``[T, heads * head_pad]`` and, when there is no ``k_pool``, the keys ``[T, kv_heads * head_pad]``
+    (else None)."""
+    T = x.shape[0]
+    if x.stride(1) != 1:
+        raise KernelLibraryError("qk_prep: rows of x must be dense")
+    hi, lo = (_rotary_rows(inv_freq, rot, "qk_prep") if rot else (_c_void_p(0), _c_void_p(0)))
+    q = torch.empty((T, heads * head_pad), dtype=q_dtype, device=x.device)
+    k = None
+    if k_pool is None:
+        k = torch.empty((T, kv_heads * head_pad), dtype=k_dtype or q_dtype, device=x.device)
+    lam, v_src = mix if mix is not None else (None, None)
+    if v_src is not None and v_src.stride(1) != 1:
+        raise KernelLibraryError("qk_prep: rows of the mixed-in values must be dense")
+    _check(library().exl3_qk_prep(
+        _ptr(x), _c_int(dtype_code(x.dtype)), _c_int64(x.stride(0)), _c_int(q_off), _c_int(k_off), _c_int(v_off),
+        _c_int(T), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(value_dim), _c_int(head_pad),
+        _c_int(value_pad), _c_int(norm), _ptr(q_w), _ptr(k_w), _c_int(dtype_code(q_w.dtype) if q_w is not None else 0),
+        _c_float(eps), _c_int(rot), _c_int(layout), hi, lo, _c_float(mscale), _c_float(k_mul), _ptr(lam),
+        _c_int(dtype_code(lam.dtype) if lam is not None else 0), _ptr(v_src),
+        _c_int(dtype_code(v_src.dtype) if v_src is not None else 0),
+        _c_int64(v_src.stride(0) if v_src is not None else 0), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table),
+        _c_int(block_table.stride(0) if block_table is not None else 0), _c_int(page), _ptr(q),
+        _c_int(dtype_code(q.dtype)), _ptr(k), _c_int(dtype_code(k.dtype) if k is not None else 0), _ptr(k_pool),
+        _ptr(v_pool), _c_int(dtype_code(k_pool.dtype) if k_pool is not None else 0), _stream()), "qk_prep")
+    return q, k
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, prev: torch.Tensor, tok_seq: torch.Tensor, row_start: torch.Tensor,
+                slot_ids: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]`` for the ``n`` rows of ``mu [n, H]``; the row before a
+    sequence's first token of the step comes from ``prev`` (float32 ``[slots, H]``) and the step's last row is
+    left there (see linear_scan.cu)."""
+    T, H = h.shape
+    _contig(h, "h")
+    _contig(mu, "mu")
+    if prev.dtype != torch.float32 or prev.shape[1] != H or mu.shape[1] != H:
+        raise KernelLibraryError("token_shift: prev must be float32 [slots, H] and mu [n, H]")
+    out = torch.empty((mu.shape[0], T, H), dtype=out_dtype, device=h.device)
+    _check(library().exl3_token_shift(
+        _ptr(h), _c_int(dtype_code(h.dtype)), _ptr(mu), _c_int(dtype_code(mu.dtype)), _c_int(mu.shape[0]), _ptr(prev),
+        _ptr(tok_seq), _ptr(row_start), _ptr(slot_ids), _ptr(out), _c_int(dtype_code(out.dtype)), _c_int(T), _c_int(H),
+        _stream()), "token_shift")
+    return out
+
+
+def linear_scan_scratch_bytes(rows: int, T: int, heads: int, dk: int, dv: int, max_new: int) -> int:
+    lib = library()
+    lib.exl3_linear_scan_scratch_bytes.restype = _c_size_t
+    return int(lib.exl3_linear_scan_scratch_bytes(_c_int(rows), _c_int(T), _c_int(heads), _c_int(dk), _c_int(dv),
+                                                  _c_int(max_new)))
+
+
+def linear_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor,
+                slot_ids: torch.Tensor, row_start: torch.Tensor, rows: int, heads: int, dk: int, dv: int, max_new: int,
+                wraw: Optional[torch.Tensor] = None, w0: Optional[torch.Tensor] = None,
+                u: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None,
+                scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The recurrence with a matrix state per head over a step's packed tokens (see linear_scan.cu).  ``r``, ``k``
+    ``[T, heads * dk]`` and ``v [T, heads * dv]`` may be views with their own row pitch; ``state`` float32 ``[slots,
+    heads, dk, dv]`` is read and written at ``slot_ids``.  Mode 0: decays ``exp(-exp(wraw + w0))`` per token and key
+    channel and the bonus ``u``; mode 1: ``decay`` float32 ``[heads]``.  Returns float32 ``[T, heads * dv]``."""
+    T = r.shape[0]
+    for t, name in ((r, "r"), (k, "k"), (v, "v"), (wraw, "wraw")):
+        if t is not None and t.stride(1) != 1:
+            raise KernelLibraryError(f"linear_scan: rows of {name} must be dense")
+    if r.dtype != k.dtype:
+        raise KernelLibraryError("linear_scan: r and k differ in element type")
+    _contig(state, "state")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, dk, dv):
+        raise KernelLibraryError(f"linear_scan: state {tuple(state.shape)} must be float32 [slots, {heads}, {dk}, {dv}]")
+    if mode == 0 and (w0.dtype != u.dtype or w0.numel() != heads * dk or u.numel() != heads * dk):
+        raise KernelLibraryError("linear_scan: w0 and u must hold heads * dk values of one type")
+    if mode == 1 and (decay.dtype != torch.float32 or decay.numel() != heads):
+        raise KernelLibraryError("linear_scan: decay must be float32 [heads]")
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=r.device)
+    _check(library().exl3_linear_scan(
+        _c_int(mode), _ptr(r), _c_int64(r.stride(0)), _ptr(k), _c_int64(k.stride(0)), _c_int(dtype_code(r.dtype)),
+        _ptr(v), _c_int64(v.stride(0)), _c_int(dtype_code(v.dtype)), _ptr(wraw),
+        _c_int64(wraw.stride(0) if wraw is not None else 0), _c_int(dtype_code(wraw.dtype) if wraw is not None else 0),
+        _ptr(w0), _ptr(u), _c_int(dtype_code(w0.dtype) if w0 is not None else 0), _ptr(decay), _ptr(state),
+        _ptr(slot_ids), _ptr(row_start), _ptr(out), _c_int(rows), _c_int(T), _c_int(heads), _c_int(dk), _c_int(dv),
+        _c_int(max_new), _ptr(scratch),
+        _c_size_t(0 if scratch is None else scratch.numel() * scratch.element_size()), _stream()), "linear_scan")
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, w: Optional[torch.Tensor], gate: Optional[torch.Tensor], eps: float, heads: int,
+                   dv: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``o [T, heads * dv]`` (float32) head by head divided by its root mean square, times ``w [heads * dv]`` and
+    ``silu(gate [T, heads * dv])`` where given."""
+    T = o.shape[0]
+    _contig(o, "o")
+    if o.dtype != torch.float32 or o.shape[1] != heads * dv:
+        raise KernelLibraryError("head_norm_gate: o must be float32 [T, heads * dv]")
+    if gate is not None and gate.stride(1) != 1:
+        raise KernelLibraryError("head_norm_gate: rows of the gate must be dense")
+    out = torch.empty((T, heads * dv), dtype=out_dtype, device=o.device)
+    _check(library().exl3_head_norm_gate(
+        _ptr(o), _ptr(w), _c_int(dtype_code(w.dtype) if w is not None else 0), _ptr(gate),
+        _c_int(dtype_code(gate.dtype) if gate is not None else 0), _c_int64(gate.stride(0) if gate is not None else 0),
+        _c_float(eps), _ptr(out), _c_int(dtype_code(out.dtype)), _c_int(T), _c_int(heads), _c_int(dv), _stream()),
+        "head_norm_gate")
+    return out
+
+
+def normed_sum2(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float,
+                coef: float) -> torch.Tensor:
+    """``coef * (rmsnorm(a) * wa + rmsnorm(b) * wb)`` row by row, float32."""
+    T, H = a.shape
+    _contig(a, "a")
+    _contig(b, "b")
+    if a.dtype != b.dtype or a.shape != b.shape or wa.dtype != wb.dtype or wa.numel() != H or wb.numel() != H:
+        raise KernelLibraryError("normed_sum2: a and b, and their weights, must agree in shape and type")
+    out = torch.empty((T, H), dtype=torch.float32, device=a.device)
+    _check(library().exl3_normed_sum2(_ptr(a), _ptr(b), _c_int(dtype_code(a.dtype)), _ptr(wa), _ptr(wb),
+                                      _c_int(dtype_code(wa.dtype)), _c_float(eps), _c_float(coef), _ptr(out),
+                                      _c_int(T), _c_int(H), _stream()), "normed_sum2")
+    return out
+
+
+ACTIVATION_KINDS = {"gelu": 0, "gelu_tanh": 1, "tanh": 2}
+
+
+def activation(z: torch.Tensor, out_dtype: torch.dtype, kind: str) -> torch.Tensor:
+    """An activation of every element, float32 inside: ``gelu`` (exact, by erf), ``gelu_tanh`` (the tanh formula)
+    or ``tanh``."""
+    _contig(z, "z")
+    out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+    _check(library().exl3_activation(_ptr(z), _c_int(dtype_code(z.dtype)), _ptr(out), _c_int(dtype_code(out.dtype)),
+                                     _c_int64(z.numel()), _c_int(ACTIVATION_KINDS[kind]), _stream()), "activation")
+    return out
+
+
 def attn_latent_supported(dtype: torch.dtype, dk: int, dv: int, page: int) -> bool:
     """Whether the tensor-core kernel for latent rows takes these sizes."""
     return (dtype == torch.bfloat16 and page == 64 and dk % 16 == 0 and dv % 16 == 0 and dv <= min(dk, 512)

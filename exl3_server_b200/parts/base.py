@@ -11,7 +11,8 @@ Interfaces (duck-typed; the classes below only document them):
                    positions into q and k inside ``qkv`` and writes k, v to the cache view
                    (when the view owns its storage).
 ``Mixer``          ``tensor_specs(spec, prefix)``; ``__init__(spec, tensors, prefix, ctx)``;
-                   ``cache_request() -> KVRequest | None``; ``state_request() -> StateRequest | None``;
+                   ``cache_request() -> KVRequest | None``; ``state_request() -> StateRequest | None``
+                   (or a tuple of requests: ``state`` is then a tuple of tensors);
                    ``forward(x, batch, kv, state) -> y`` with x, y ``[tokens, width]``.
 ``FeedForward``    ``tensor_specs(spec, prefix)``; ``__init__(spec, tensors, prefix, ctx)``;
                    ``forward(x, batch) -> y``.
@@ -41,12 +42,15 @@ class KVRequest:
     """Keys and values for every position (window 0) or the last ``window``.  ``value_dim`` is the width of a
     value per head when it differs from the key's (0: the same), as in mixers that keep narrow keys or a
     compressed value.  ``values_in_keys``: there is no pool of values; a mixer whose values are part of what it
-    keeps as keys (one latent row per token) gets the key pool as both."""
+    keeps as keys (one latent row per token) gets the key pool as both.  ``chunk`` > 0: a query sees only the keys
+    of its own block of ``chunk`` positions (counted from the sequence's start), so the cache gives back the pages
+    that lie wholly before the block of the next position."""
     kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: int = 0
     values_in_keys: bool = False
+    chunk: int = 0
 
 
 @dataclass(frozen=True)

@@ -9,6 +9,10 @@ norm's kernel.
 output: ``h += norm1(mixer(h))`` then ``h += norm2(ff(h))``.  The norm, the add
 (float32) and the cast of the new residual for the next sublayer are one kernel.
 A layer of this kind may have no feed-forward at all.
+
+``sandwich``: a norm on both sides of each sublayer: ``h += rho * norm1b(mixer(norm1(h)))`` then
+``h += rho * norm2b(ff(norm2(h)))``.  The constant ``rho`` is a parameter of the output norms (their ``scale``), so
+the second norm, the constant and the add (float32) are one kernel, as in ``outnorm``.
 """
 from __future__ import annotations
 
@@ -78,5 +82,33 @@ class OutNormBlock:
                    if p is not None and hasattr(p, "weight_bytes"))
 
 
+class SandwichBlock:
+    def __init__(self, spec: LayerSpec, mixer, feed_forward, mixer_norm, feed_forward_norm, out_norms=(None, None)):
+        self.spec = spec
+        self.mixer = mixer
+        self.feed_forward = feed_forward              # None: the layer is its mixer only
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+        self.mixer_out_norm, self.feed_forward_out_norm = out_norms
+        if self.mixer_out_norm is None or (feed_forward is not None and self.feed_forward_out_norm is None):
+            raise ValueError("sandwich: every sublayer needs a norm on its output")
+        for n in (self.mixer_out_norm, self.feed_forward_out_norm):
+            if n is not None and float(n.spec.params.get("scale", 1.0)) != float(spec.residual_scale):
+                raise ValueError("sandwich: the output norms' scale must be the layer's residual scale")
+
+    def forward(self, stream: ResidualStream, batch, kv, state) -> None:
+        x = self.mixer_norm.add_norm(stream)
+        self.mixer_out_norm.add_normed(stream, self.mixer.forward(x, batch, kv, state), want_x=False)
+        if self.feed_forward is not None:
+            x = self.feed_forward_norm.add_norm(stream)
+            self.feed_forward_out_norm.add_normed(stream, self.feed_forward.forward(x, batch), want_x=False)
+
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in (self.mixer, self.feed_forward, self.mixer_norm, self.feed_forward_norm,
+                                              self.mixer_out_norm, self.feed_forward_out_norm)
+                   if p is not None and hasattr(p, "weight_bytes"))
+
+
 register_arrangement("prenorm", PreNormBlock)
+register_arrangement("sandwich", SandwichBlock)
 register_arrangement("outnorm", OutNormBlock)

@@ -19,7 +19,7 @@ import torch
 
 from ..ops import kernels as K
 from ..weights.loader import TensorSpec
-from .base import BuildContext, ResidualStream
+from .base import BuildContext, ResidualStream, StateRequest
 from .linear import Linear
 from .registry import register_embedding, register_head
 from .spec import EmbeddingSpec, HeadSpec
@@ -70,5 +70,42 @@ class Head:
         return self.linear.weight_bytes()
 
 
+class HashedPairEmbedding:
+    """``h0[t] = E[id_t] + P[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets]``: the token's row plus a row of a
+    second table picked by a hash of the token and the one before it; a sequence's first token takes the second
+    table's last row (number ``buckets``).  The token before a step's first token is per-sequence state (an int32
+    per slot) that the kernel keeps up.  Parameters of the spec: ``pair_name``, ``buckets``, ``mul_prev``,
+    ``mul_cur``."""
+
+    takes_batch = True
+
+    @staticmethod
+    def tensor_specs(spec: EmbeddingSpec) -> List[TensorSpec]:
+        return [TensorSpec(spec.name, (spec.vocab, spec.width)),
+                TensorSpec(spec.params["pair_name"], (int(spec.params["buckets"]) + 1, spec.width))]
+
+    def __init__(self, spec: EmbeddingSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
+        if float(spec.scale) != 1.0:
+            raise ValueError("hashed pair embedding: no scale on the sum of two rows")
+        self.spec = spec
+        self.table = tensors[spec.name].to(ctx.dtype).contiguous()
+        self.pairs = tensors[spec.params["pair_name"]].to(ctx.dtype).contiguous()
+        self.buckets = int(spec.params["buckets"])
+        self.mul_prev, self.mul_cur = int(spec.params["mul_prev"]), int(spec.params["mul_cur"])
+
+    def state_request(self) -> StateRequest:
+        return StateRequest((), torch.int32)
+
+    def forward(self, token_ids: torch.Tensor, batch, state: Optional[torch.Tensor]) -> ResidualStream:
+        if state is None:
+            raise RuntimeError("the hashed pair embedding needs its per-sequence state")
+        return ResidualStream(K.embed_hashed(token_ids, batch.tok_pos, batch.tok_seq, batch.row_start, batch.slot_ids,
+                                             self.table, self.pairs, self.buckets, self.mul_prev, self.mul_cur, state))
+
+    def weight_bytes(self) -> int:
+        return (self.table.numel() + self.pairs.numel()) * self.table.element_size()
+
+
 register_embedding("table", Embedding)
+register_embedding("table_hashed_pair", HashedPairEmbedding)
 register_head("linear", Head)

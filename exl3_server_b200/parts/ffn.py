@@ -6,7 +6,7 @@ up projections are one fused matrix; the product ``silu(g) * u`` is float32
 inside its kernel.
 
 ``dense``: ``y = act(r Wu^T) Wd^T`` with an activation named in the spec's
-``params["activation"]``.  ``xielu`` has two learned numbers ``p, q`` (tensor
+``params["activation"]``: ``xielu``, ``gelu`` (exact, by erf) or ``gelu_tanh``.  ``xielu`` has two learned numbers ``p, q`` (tensor
 ``act``): ``softplus(p) z^2 + z/2`` for ``z > 0`` and
 ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z/2`` otherwise; it is computed in
 float32 (from float32 results of the up projection where the projection's kernel has them); for steps of few
@@ -90,10 +90,28 @@ def _xielu_fused(linear: Linear, x: torch.Tensor, tensors, out_dtype):
     return linear.xielu(x, *tensors["act.constants"], out_dtype)
 
 
+def _gelu(z: torch.Tensor, tensors, out_dtype):
+    return K.activation(z, out_dtype, "gelu")
+
+
+def _gelu_tanh(z: torch.Tensor, tensors, out_dtype):
+    return K.activation(z, out_dtype, "gelu_tanh")
+
+
+def _no_fused(linear: Linear, x: torch.Tensor, tensors, out_dtype):
+    return None
+
+
+def _no_prepare(tensors) -> None:
+    return None
+
+
 # name -> (parameter tensors as (suffix, shape), function(z, {suffix: tensor}, out_dtype),
 #          function(linear, x, {suffix: tensor}, out_dtype) -> activated projection or None,
 #          function({suffix: tensor}) called once when the part is built)
-ACTIVATIONS = {"xielu": ((("act", (2,)),), _xielu, _xielu_fused, _xielu_prepare)}
+ACTIVATIONS = {"xielu": ((("act", (2,)),), _xielu, _xielu_fused, _xielu_prepare),
+               "gelu": ((), _gelu, _no_fused, _no_prepare),               # z/2 (1 + erf(z / sqrt 2))
+               "gelu_tanh": ((), _gelu_tanh, _no_fused, _no_prepare)}     # z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 
 
 class DenseFeedForward:

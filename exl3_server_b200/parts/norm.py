@@ -6,7 +6,11 @@
 residual add ``h += scale * y`` are float32.
 
 The same norm also serves layers that norm a sublayer's output instead of its
-input (``add_normed``: ``h += rmsnorm(y) * w``; the ``outnorm`` arrangement).
+input (``add_normed``: ``h += rmsnorm(y) * w``; the ``outnorm`` and ``sandwich`` arrangements).
+
+Parameters of the spec: ``suffix`` (the tensor's name after the prefix), ``one_plus`` (the stored weight lies
+around zero and the factor is ``1 + w``) and ``scale`` (a constant on the norm's output, such as a multiplier of
+the residual branch).
 """
 from __future__ import annotations
 
@@ -29,6 +33,11 @@ class RMSNorm:
     def __init__(self, spec: NormSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
         self.spec = spec
         w = tensors[prefix + spec.params.get("suffix", "weight")]     # the tensor's name is prefix + suffix
+        one_plus, scale = bool(spec.params.get("one_plus", False)), float(spec.params.get("scale", 1.0))
+        if one_plus or scale != 1.0:
+            # a weight stored around zero (the factor is 1 + w) and a constant on the norm's output: both folded
+            # into one float32 weight when the model is built
+            w = ((w.float() + 1.0) if one_plus else w.float()) * scale
         # a weight stored in 32-bit stays 32-bit; the kernel reads either
         self.weight = w.contiguous() if w.dtype == torch.float32 else w.to(ctx.dtype).contiguous()
         self.out_dtype = ctx.dtype
@@ -50,13 +59,18 @@ class RMSNorm:
         return K.add_rmsnorm(stream.h, y, s, self.weight, self.spec.eps, self.out_dtype,
                              out_scale=out_scale, rows=rows)
 
-    def add_normed(self, stream: ResidualStream, y: Optional[torch.Tensor]) -> torch.Tensor:
+    def add_normed(self, stream: ResidualStream, y: Optional[torch.Tensor], want_x: bool = True) -> Optional[torch.Tensor]:
         """The norm on a sublayer's OUTPUT: ``h += y * rsqrt(mean(y^2) + eps) * w`` in float32; returns the new
         residual in the activation type, which the next sublayer reads (``h`` itself in the float32 path).  With
-        ``y`` None nothing is added and the residual is only handed over."""
+        ``y`` None nothing is added and the residual is only handed over.  ``want_x`` False: nothing is returned
+        (the next sublayer reads a norm of the residual, not the residual)."""
         if stream.pending is not None:
             raise RuntimeError("the residual stream holds an output that was not folded in")
         stream.normed = None
+        if not want_x:
+            stream.act = None
+            K.norm_add(stream.h, y, self.weight, self.spec.eps, None)
+            return None
         x_dtype = None if self.out_dtype == torch.float32 else self.out_dtype
         x = K.norm_add(stream.h, y, self.weight if y is not None else None, self.spec.eps, x_dtype)
         stream.act = x if x is not None else stream.h

@@ -67,6 +67,10 @@ class LayerSpec:
     residual_scale: float         # sublayer outputs are multiplied by this before the add
     # tensor-name prefixes in the checkpoint, by role
     names: Dict[str, str] = field(default_factory=dict, hash=False, compare=False)
+    # arrangements with a norm on both sides of a sublayer ("sandwich"): the norms on the sublayers' outputs
+    # (names under "mixer_out_norm" / "feed_forward_out_norm")
+    mixer_out_norm: Optional[NormSpec] = None
+    feed_forward_out_norm: Optional[NormSpec] = None
 
 
 @dataclass(frozen=True)

@@ -32,6 +32,9 @@ class TensorSpec:
     kind: str = "float"            # "float" or "int"
     optional: bool = False
     init: str = "normal"           # for random weights: "normal", "ones", "zeros"
+    # a dimension of -1 in ``shape`` is whatever the checkpoint has (a size that no configuration key gives, such
+    # as the rank of a low-rank pair); random weights take ``free_dim`` there
+    free_dim: int = 16
 
 
 _FLOATS = (torch.float16, torch.bfloat16, torch.float32, torch.float64)
@@ -69,8 +72,10 @@ def check_manifest(manifest: Sequence[TensorSpec], found: Dict[str, Tuple[int, .
         raise WeightsError("model lists a tensor twice: " + ", ".join(sorted(set(dup))))
     missing = [n for n, s in wanted.items() if n not in found and not s.optional]
     unexpected = [n for n in found if n not in wanted and not any(fnmatchcase(n, p) for p in ignorable)]
-    wrong = [(n, found[n], wanted[n].shape) for n in wanted
-             if n in found and tuple(found[n]) != tuple(wanted[n].shape)]
+    def fits(got, exp) -> bool:
+        return len(got) == len(exp) and all(e == -1 or g == e for g, e in zip(got, exp))
+
+    wrong = [(n, found[n], wanted[n].shape) for n in wanted if n in found and not fits(tuple(found[n]), tuple(wanted[n].shape))]
     if not (missing or unexpected or wrong):
         return
     lines = ["checkpoint does not fit the model:"]

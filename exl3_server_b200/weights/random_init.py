@@ -34,10 +34,11 @@ def random_tensors(manifest: Sequence[TensorSpec], seed: int, std: float = 0.02,
             continue
         g = torch.Generator(device=device)
         g.manual_seed(_tensor_seed(seed, spec.name))
+        shape = tuple(spec.free_dim if d == -1 else d for d in spec.shape)
         if spec.kind == "int":
-            yield spec.name, torch.zeros(spec.shape, dtype=torch.int32, device=device)
+            yield spec.name, torch.zeros(shape, dtype=torch.int32, device=device)
             continue
-        x = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
+        x = torch.randn(shape, generator=g, dtype=torch.float32, device=device)
         if spec.init == "ones":
             x = 1.0 + x * norm_std if norm_std is not None else x * std
         else:                                           # "normal", and biases when asked for
