@@ -1,0 +1,314 @@
+"""The Nikodra decoder in the engine against the plain implementation (tests/plain_nikodra.py): each mechanism alone,
+whole prompts against token-by-token decoding, portions, unequal batches with slots, pages and state rows used again,
+keys far back, at page borders and on both sides of a block's edge, first tokens, long decoding, generation through
+the entry point, the replay program; float32 and bfloat16, on configurations that differ in every size and option."""
+import json
+import os
+import shutil
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, batched_trace, random_requests, rel_err, run_trace, tail_trace, whole_trace
+from nikodra_configs import CONFIGS, make_nikodra
+from plain_nikodra import PlainNikodra
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"mixed": [1, 2, 9, 64, 65, 150], "odd": [1, 3, 20, 64, 66, 131], "wide": [3, 17, 63, 128, 129, 300],
+           "only_attention": [1, 2, 31, 64, 129, 140], "only_parallel": [1, 2, 31, 64, 129, 141],
+           "only_wkv": [1, 2, 31, 64, 129, 140], "only_embedding": [1, 2, 31, 64, 129, 140]}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("nikodra")
+    return {name: make_nikodra(name, str(root / name)) for name in CONFIGS}
+
+
+_plain = {}
+
+
+def plain(folder):
+    if folder not in _plain:
+        _plain[folder] = PlainNikodra(folder)
+    return _plain[folder]
+
+
+def engine_for(folder, dtype, max_tokens=2048):
+    from exl3_server_b200 import Engine
+    return Engine.from_folder(folder, dtype=dtype, max_tokens=max_tokens)
+
+
+def check(got, want, dtype, what):
+    assert set(got) == set(want)
+    for rid in want:
+        assert got[rid].shape == want[rid].shape, (what, rid)
+        assert np.isfinite(got[rid]).all(), (what, rid)
+        err = rel_err(got[rid], want[rid])
+        if err > TOL[dtype]:
+            per_pos = np.max(np.abs(got[rid] - want[rid]), axis=1) / np.max(np.abs(want[rid]))
+            first = int(np.argmax(per_pos > TOL[dtype]))
+            raise AssertionError(f"{what}: request {rid} (length {len(per_pos)}) differs from the plain "
+                                 f"implementation by {err:.3e} (bound {TOL[dtype]:.0e}); first wrong position {first}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_decoded_and_batched(folders, name, dtype):
+    folder = folders[name]
+    requests = random_requests(CONFIGS[name].vocab, LENGTHS[name], seed=3)
+    pm = plain(folder)
+    want = {rid: pm.logits(t).numpy() for rid, t in requests.items()}
+    eng = engine_for(folder, dtype)
+    check(run_trace(eng, whole_trace(requests)), want, dtype, "whole")
+    check(run_trace(eng, tail_trace(requests, 32)), want, dtype, "last 32 one by one")
+    # everything but the first token decoded: the prompt path and the one-token path must walk the same sums
+    short = {rid: t for rid, t in requests.items() if len(t) <= 70}
+    check(run_trace(eng, tail_trace(short, 1000)), {rid: want[rid] for rid in short}, dtype, "token by token")
+    ids = list(requests)
+    # two batches one after the other, so that slots, pages and state rows are used again
+    batches = [[ids[5], ids[0], ids[2], ids[3]], [ids[1], ids[4], ids[0]]]
+    prompt_len = {rid: max(1, len(requests[rid]) - k) for rid, k in zip(ids, (0, 1, 4, 40, 33, 70))}
+    check(run_trace(eng, batched_trace(requests, batches, prompt_len)),
+          {rid: want[rid] for b in batches for rid in b}, dtype, "batched")
+    assert eng.cache.tokens_held() == 0
+    eng.check_kernels()
+
+
+@pytest.mark.parametrize("name", ["mixed", "wide"])
+def test_float32_cuttings_agree_closely(folders, name):
+    requests = random_requests(CONFIGS[name].vocab, LENGTHS[name], seed=5)
+    eng = engine_for(folders[name], "float32")
+    a = run_trace(eng, whole_trace(requests))
+    b = run_trace(eng, tail_trace(requests, 32))
+    for rid in requests:
+        assert rel_err(b[rid], a[rid]) <= 2e-6, rid
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_portions_of_a_prompt(folders, name, dtype):
+    """A prompt fed in portions of many sizes, down to two tokens, some ending on a page border, on a block's edge
+    (50 and 7 positions) and inside one, and one long enough for the recurrences' chunks to run side by side."""
+    from exl3_server_b200 import StepEntry
+    folder = folders[name]
+    toks = random_requests(CONFIGS[name].vocab, [430], seed=9)["r0"]
+    want = plain(folder).logits(toks).numpy()
+    eng = engine_for(folder, dtype)
+    for cuts in ([2, 2, 60, 3, 61, 2, 100, 200], [64, 64, 2, 37, 63, 200], [7, 121, 2, 2, 2, 96, 199, 1], [429, 1],
+                 [50, 50, 50, 130, 150], [1, 300, 129]):
+        assert sum(cuts) == len(toks)
+        s = eng.open()
+        got, at = [], 0
+        for n in cuts:
+            got.append(eng.step([StepEntry(s, toks[at:at + n], "all")]).float().cpu().numpy())
+            at += n
+        eng.close(s)
+        err = rel_err(np.concatenate(got), want)
+        assert err <= TOL[dtype], (cuts, err)
+    assert eng.cache.tokens_held() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unequal_portions_in_one_batch(folders, dtype):
+    """Rows that go on by portions of different sizes in the same steps, beside a row that starts."""
+    from exl3_server_b200 import StepEntry
+    folder = folders["mixed"]
+    reqs = random_requests(CONFIGS["mixed"].vocab, [150, 90, 40], seed=13)
+    pm = plain(folder)
+    want = {r: pm.logits(t).numpy() for r, t in reqs.items()}
+    eng = engine_for(folder, dtype)
+    sa, sb = eng.open(), eng.open()
+    got = {r: [] for r in reqs}
+    out = eng.step([StepEntry(sa, reqs["r0"][:70], "all"), StepEntry(sb, reqs["r1"][:3], "all")]).float().cpu().numpy()
+    got["r0"].append(out[:70]); got["r1"].append(out[70:])
+    sc = eng.open()
+    out = eng.step([StepEntry(sb, reqs["r1"][3:66], "all"), StepEntry(sc, reqs["r2"], "all"),
+                    StepEntry(sa, reqs["r0"][70:72], "all")]).float().cpu().numpy()
+    got["r1"].append(out[:63]); got["r2"].append(out[63:103]); got["r0"].append(out[103:])
+    eng.close(sc)
+    out = eng.step([StepEntry(sa, reqs["r0"][72:], "all"), StepEntry(sb, reqs["r1"][66:], "all")]).float().cpu().numpy()
+    got["r0"].append(out[:78]); got["r1"].append(out[78:])
+    for r in reqs:
+        assert rel_err(np.concatenate(got[r]), want[r]) <= TOL[dtype], r
+
+
+def _marked_model(src, folder, name):
+    """A copy of a one-layer model in which one token's key stands out for every query.  Feature 0 of the model is
+    on for the marked token only and feature 1 for every token (the other embedding features stay random); the key
+    matrix sends feature 0, and the query matrix feature 1, to the same head features (the second half of each head,
+    which the attention layer's partial rotation leaves alone), so the marked key's score is some twenty times the
+    spread of the others' wherever the query stands."""
+    from safetensors import safe_open
+    from exl3_server_b200.weights.safetensors_io import write_safetensors
+    os.makedirs(folder)
+    shutil.copy(os.path.join(src, "config.json"), folder)
+    with safe_open(os.path.join(src, "model.safetensors"), framework="pt") as f:
+        tensors = {k: f.get_tensor(k).float() for k in f.keys()}
+    marked = 77
+    tensors["embed"][:, 0] = 0.0
+    tensors["embed"][:, 1] = 0.5
+    tensors["embed"][marked, 0] = 2.0
+    tensors["l0.norm1"][:2] = 0.0
+    qn, kn = ("l0.mix.left.q", "l0.mix.left.k") if name == "only_parallel" else ("l0.mix.q", "l0.mix.k")
+    m = CONFIGS[name].layers[0].mixer
+    d = (m["left"] if name == "only_parallel" else m)["dim"]
+    for w, col in ((tensors[qn], 1), (tensors[kn], 0)):
+        w[:, col] = 0.0
+        w.view(-1, d, w.shape[1])[:, d // 2:, col] = 3.0
+    write_safetensors(os.path.join(folder, "model.safetensors"), ((k, v.to(torch.bfloat16)) for k, v in tensors.items()),
+                      metadata={"format": "pt"})
+    return marked
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name, places", [("only_attention", [0, 1, 63, 64, 127, 128, 300]),
+                                           ("only_parallel", [630, 629, 639, 640, 690, 699])])
+def test_a_key_that_stands_out(folders, tmp_path, name, places, dtype):
+    """The marked key sits first, second, on both sides of page borders and hundreds of tokens back (plain attention),
+    and just outside, first in, on a page border inside and last in the block of 70 positions that the last queries
+    belong to (630 .. 699); losing it, reading a neighbour instead or seeing it across a block's edge changes the
+    logits by far more than the bound."""
+    folder = str(tmp_path / "m")
+    marked = _marked_model(folders[name], folder, name)
+    pm = PlainNikodra(folder)
+    vocab = CONFIGS[name].vocab
+    base = [t if t != marked else 5 for t in random_requests(vocab, [700], seed=21)["r0"]]
+    eng = engine_for(folder, dtype)
+    for place in places:
+        toks = list(base)
+        toks[place] = marked
+        want = pm.logits(toks).numpy()
+        visible = name == "only_attention" or place >= 630
+        gap = rel_err(pm.logits(base).numpy()[-20:], want[-20:])
+        if visible:
+            assert gap > 0.3, (place, gap)                # the test can see the key
+        got = run_trace(eng, whole_trace({"a": toks}))["a"]
+        assert rel_err(got, want) <= TOL[dtype], ("whole", place)
+        got = run_trace(eng, tail_trace({"a": toks}, 75))["a"]
+        assert rel_err(got, want) <= TOL[dtype], ("decoded", place)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_long_decoding(folders, name, dtype):
+    """Three tokens of prompt, then 200 decoded one by one over three page borders and several blocks' edges, two
+    sequences side by side."""
+    from exl3_server_b200 import StepEntry
+    folder = folders[name]
+    reqs = random_requests(CONFIGS[name].vocab, [203, 180], seed=17)
+    pm = plain(folder)
+    want = [pm.logits(reqs["r0"]).numpy(), pm.logits(reqs["r1"]).numpy()]
+    eng = engine_for(folder, dtype)
+    s = [eng.open(), eng.open()]
+    got = [[], []]
+    out = eng.step([StepEntry(s[0], reqs["r0"][:3], "all"), StepEntry(s[1], reqs["r1"][:3], "all")]).float().cpu().numpy()
+    got[0].append(out[:3]); got[1].append(out[3:])
+    for i in range(3, 203):
+        live = [k for k in (0, 1) if i < len(reqs[f"r{k}"])]
+        out = eng.step([StepEntry(s[k], [reqs[f"r{k}"][i]], "all") for k in live]).float().cpu().numpy()
+        for j, k in enumerate(live):
+            got[k].append(out[j:j + 1])
+    for k in (0, 1):
+        assert rel_err(np.concatenate(got[k]), want[k]) <= TOL[dtype], k
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_reused_slot_shows_nothing_of_its_former_owner(folders, dtype):
+    """A sequence's state rows (matrix states, the input and the token before) and pages go to the next sequence;
+    the next one must start from zero state and see none of the old rows, also when it is shorter than the old one."""
+    from exl3_server_b200 import StepEntry
+    folder = folders["mixed"]
+    reqs = random_requests(CONFIGS["mixed"].vocab, [190, 30], seed=23)
+    want = plain(folder).logits(reqs["r1"]).numpy()
+    eng = engine_for(folder, dtype, max_tokens=256)
+    for _ in range(3):
+        s = eng.open()
+        eng.step([StepEntry(s, reqs["r0"], None)])
+        eng.close(s)
+        s2 = eng.open()
+        assert s2 == s
+        got = [eng.step([StepEntry(s2, reqs["r1"][:9], "all")]).float().cpu().numpy()]
+        for t in reqs["r1"][9:]:
+            got.append(eng.step([StepEntry(s2, [t], "all")]).float().cpu().numpy())
+        eng.close(s2)
+        assert rel_err(np.concatenate(got), want) <= TOL[dtype]
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("name", ["mixed", "odd", "wide"])
+def test_greedy_generation_through_the_entry_point(folders, name):
+    from exl3_server_b200 import GenerateOptions
+    folder = folders[name]
+    prompts = list(random_requests(CONFIGS[name].vocab, [5, 70, 1, 33], seed=29).values())
+    eng = engine_for(folder, "float32")
+    res = eng.generate(prompts, GenerateOptions(max_tokens=24, ignore_eos=True, max_batch=3))
+    pm = plain(folder)
+    for p, r in zip(prompts, res):
+        assert r.tokens == pm.greedy(p, 24)
+        assert r.finish_reason == "length"
+    assert eng.cache.tokens_held() == 0
+    # bfloat16: the same call runs and every token is in range (near-ties may fall the other way)
+    eng = engine_for(folder, "bfloat16")
+    res = eng.generate(prompts, GenerateOptions(max_tokens=24, ignore_eos=True))
+    assert all(len(r.tokens) == 24 and all(0 <= t < CONFIGS[name].vocab for t in r.tokens) for r in res)
+    eng.check_kernels()
+
+
+def test_residual_stream_layer_by_layer(folders):
+    """The float32 residual after every layer against the plain implementation's."""
+    from exl3_server_b200 import StepEntry
+    folder = folders["mixed"]
+    toks = random_requests(CONFIGS["mixed"].vocab, [75], seed=31)["r0"]
+    want = plain(folder).residuals(toks)[1:]
+    eng = engine_for(folder, "float32")
+    seen = []
+    for b in eng.model.blocks:
+        def wrapped(stream, batch, kv, state, f=b.forward):
+            f(stream, batch, kv, state)
+            seen.append(stream.h.clone())
+        b.forward = wrapped
+    s = eng.open()
+    eng.step([StepEntry(s, toks, None)])
+    assert len(seen) == len(want)
+    for i, (a, b) in enumerate(zip(seen, want)):
+        assert rel_err(a.cpu().numpy(), b.numpy()) <= 1e-5, i
+
+
+def test_replay_program_and_command_line(folders, tmp_path):
+    folder = folders["mixed"]
+    vocab = CONFIGS["mixed"].vocab
+    reqs = random_requests(vocab, [40, 7], seed=4)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": reqs["r0"][:38], "want": [0, 37]},
+                                {"id": "b", "tokens": reqs["r1"][:6], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": [reqs["r0"][38]], "want": [0]},
+                                {"id": "b", "tokens": [reqs["r1"][6]], "want": [0]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": [reqs["r0"][39]], "want": []}], "end": ["a"]},
+        {"step": 3, "entries": [{"id": "b", "tokens": reqs["r1"], "want": [6]}], "end": ["b"]},
+    ]
+    pm = plain(folder)
+    la, lb = pm.logits(reqs["r0"]).numpy(), pm.logits(reqs["r1"]).numpy()
+    for dtype in DTYPES:
+        out = tmp_path / dtype
+        p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                            "--out", str(out), "--max-tokens", "128"],
+                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                           timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert p.stdout.split() == ["done", "0", "done", "1", "done", "2", "done", "3"]
+        s0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, vocab)
+        s1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(-1, vocab)
+        s3 = np.fromfile(out / "3.f32", dtype="<f4").reshape(-1, vocab)
+        assert rel_err(s0, la[[0, 37]]) <= TOL[dtype]
+        assert rel_err(s1, np.stack([la[38], lb[6]])) <= TOL[dtype]
+        assert rel_err(s3, lb[6:7]) <= TOL[dtype]
+    p = subprocess.run([sys.executable, "-m", "exl3_server_b200", "--model", folder, "-p", "5,6,7", "--max-tokens", "5",
+                        "--ignore-eos", "--dtype", "float32"], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert p.stdout.strip() == ",".join(map(str, pm.greedy([5, 6, 7], 5)))
