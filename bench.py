@@ -26,11 +26,13 @@ fallback.
 the size tables and prints a short JSON line (for profiling small cases).
 
 ``--only designs`` measures the Rigitar decoder (latent attention, minGRU and
-dense xIELU layers) beside the Llama-family decoder at equal width, depth, head
-count and feed-forward width, with random weights: one prompt of
+dense xIELU layers) and the Nikodra decoder (attention with a sink, attention in
+blocks beside retention, wkv recurrences, dense GELU layers) beside the
+Llama-family decoder at equal width, depth, head count and feed-forward width,
+with random weights: one prompt of
 ``--prefill-tokens`` tokens and decode steps at ``--batch`` and ``--context``,
 for each of the size pairs in ``DESIGN_SIZES`` (or the one named by
-``--design-sizes``); ``--design-arch`` runs one of the two only (for profiling).
+``--design-sizes``); ``--design-arch`` runs one of the designs only (for profiling).
 
 Only one GPU is supported: for N > 1 it says so and exits with 2.
 """
@@ -119,13 +121,31 @@ class ClockSampler:
 # Size pairs for ``--only designs``: width, layers, heads, feed-forward width, vocabulary; the Llama side has heads of
 # ``head_dim`` on ``kv_heads`` key/value heads; the Rigitar side has latent attention with these sizes in half of its
 # layers (every second of them reading the rows of the one before), minGRU of the model's width in the others, and
-# the dense feed-forward in all.
+# the dense feed-forward in all; the Nikodra side repeats attention, attention, attention in blocks of 1,024 positions
+# beside retention (states of 64 x head_dim), wkv (heads of 64), with the dense feed-forward in all.
 DESIGN_SIZES = {
     "w2048": dict(width=2048, layers=8, heads=16, ff=5632, vocab=32000, head_dim=128, kv_heads=16,
                   latent=dict(dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=512)),
     "w4096": dict(width=4096, layers=4, heads=32, ff=11008, vocab=32000, head_dim=128, kv_heads=8,
                   latent=dict(dim=128, rot_dim=64, vdim=128, q_rank=1536, kv_rank=512)),
 }
+
+
+def nikodra_config(z):
+    from exl3_server_b200.config.nikodra import NikodraConfig, NikodraLayer
+    hd = z["head_dim"]
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "v_mix": True,
+           "rot": {"base": 1000000.0, "dims": hd, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    left = {k: att[k] for k in ("heads", "kv_heads", "dim", "vdim", "scale")}
+    left["mask"] = {"size": 1024}
+    right = {"heads": z["heads"], "dim": 64, "vdim": hd, "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * i / z["heads"]) for i in range(z["heads"])],
+             "rot": {"base": 10000.0, "dims": 64}}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    kinds = [("attention", att), ("attention", att), ("parallel", {"left": left, "right": right}),
+             ("wkv", {"heads": z["width"] // 64, "dim": 64, "decay_rank": 64})]
+    layers = [NikodraLayer(kinds[i % 4][0], dict(kinds[i % 4][1]), dict(mlp)) for i in range(z["layers"])]
+    return NikodraConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, residual_mult=0.5,
+                         bigram={"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}, layers=layers)
 
 
 def design_configs(name: str):
@@ -215,6 +235,23 @@ class Rig:
 
     def kv_bytes_per_token(self):
         return sum(g.bytes_per_token(2) for g in self.engine.cache.groups)
+
+    def context_bytes(self, ctx):
+        """Bytes of cache and state that one sequence's decode step at ``ctx`` tokens of context has to move: the
+        keys and values it may see (a window or a block of positions bounds them) and its per-sequence state, read
+        and written."""
+        n = 0
+        for g in self.engine.cache.groups:
+            seen = ctx
+            if g.request.window > 0:
+                seen = min(seen, g.request.window)
+            if g.request.chunk > 0:
+                seen = min(seen, (ctx - 1) % g.request.chunk + 1)
+            n += g.bytes_per_token(2) * seen
+        for t in self.engine.cache.state.values():
+            for part in (t if isinstance(t, tuple) else (t,)):
+                n += 2 * part[0].numel() * part.element_size()
+        return n
 
     def prefill_flops(self, lengths):
         """Matrix products of every layer for all tokens, causal attention, the head on one row per prompt."""
@@ -336,8 +373,8 @@ class Rig:
 
 
 def designs(args) -> int:
-    """``--only designs``: prefill and decode throughput of the Rigitar decoder beside the Llama-family decoder of
-    equal sizes; one JSON line."""
+    """``--only designs``: prefill and decode throughput of the Rigitar and Nikodra decoders beside the Llama-family
+    decoder of equal sizes; one JSON line."""
     import torch
     torch.cuda.set_device(0)
     hbm_gbs, bf16_tf, peak_src = peaks()
@@ -350,7 +387,7 @@ def designs(args) -> int:
     for name in ([args.design_sizes] if args.design_sizes else sorted(DESIGN_SIZES)):
         rig_cfg, llama_cfg = design_configs(name)
         rec = {}
-        for arch, cfg in (("rigitar", rig_cfg), ("llama", llama_cfg)):
+        for arch, cfg in (("nikodra", nikodra_config(DESIGN_SIZES[name])), ("rigitar", rig_cfg), ("llama", llama_cfg)):
             if args.design_arch not in ("both", arch):
                 continue
             rig = Rig.of_config(f"{name}/{arch}", cfg, room, B + 1)
@@ -360,6 +397,7 @@ def designs(args) -> int:
                 r.update(prefill_ms=ms, prefill_tok_s=T / (ms / 1e3))
             if args.design_part in ("both", "decode"):
                 ms, launches, kv = rig.decode(B, C, steps, warm)
+                kv = B * rig.context_bytes(C - steps // 2)
                 gbs = (rig.model.weight_bytes() + kv) / (ms / steps / 1e3) / 1e9
                 r.update(decode_ms_per_step=ms / steps, decode_tok_s=B * steps / (ms / 1e3), decode_gb_s=gbs,
                          decode_hbm_frac=gbs / hbm_gbs, gpu_launches_per_step=int(launches) // steps)
@@ -388,8 +426,8 @@ def main() -> int:
                     help="run one part only (for profiling small cases); prints a short JSON line")
     ap.add_argument("--design-sizes", choices=sorted(DESIGN_SIZES), default=None,
                     help="with --only designs: one size pair instead of all")
-    ap.add_argument("--design-arch", choices=["both", "rigitar", "llama"], default="both",
-                    help="with --only designs: one of the two designs only")
+    ap.add_argument("--design-arch", choices=["both", "nikodra", "rigitar", "llama"], default="both",
+                    help="with --only designs: one of the designs only (both: all of them)")
     ap.add_argument("--design-part", choices=["both", "prefill", "decode"], default="both",
                     help="with --only designs: one of the two measurements only")
     args = ap.parse_args()

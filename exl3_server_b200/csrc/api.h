@@ -37,6 +37,8 @@ int exl3_gemv_bf16(const void* x, const void* w, const void* bias, void* y, int 
 
 // exl3_gemv_bf16 (epilogue 0) with the xIELU activation on its results: act_p z^2 + z / 2 for z > 0, act_n (exp(z) - 1 - z)
 // + z / 2 otherwise, with act_p = softplus(p) and act_n = 1/2 + softplus(q) given by the caller.
+int exl3_gemv_bf16_gelu(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N, int K,
+                        int kind, cudaStream_t stream);
 int exl3_gemv_bf16_act(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N, int K,
                        float act_p, float act_n, cudaStream_t stream);
 
@@ -126,6 +128,10 @@ int exl3_head_norm_gate(const float* o, const void* w, int w_dtype, const void* 
 // out[t] = coef * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb), float32 out
 int exl3_normed_sum2(const void* a, const void* b, int ab_dtype, const void* wa, const void* wb, int w_dtype, float eps,
                      float coef, float* out, int T, int H, cudaStream_t stream);
+// h += y / rms(y) * w (as exl3_norm_add) and, over the new residual, x = h / rms(h) * w2 in x's type: the norm on
+// a sublayer's output, the residual sum and the next sublayer's input norm in one kernel.
+int exl3_norm_add_norm(float* h, const void* y, int y_dtype, const void* w, int w_dtype, float eps, const void* w2,
+                       int w2_dtype, float eps2, void* x, int x_dtype, int T, int H, cudaStream_t stream);
 // kind 0: z/2 (1 + erf(z / sqrt 2)); 1: z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2: tanh(z)
 int exl3_activation(const void* z, int z_dtype, void* out, int out_dtype, int64_t n, int kind, cudaStream_t stream);
 
@@ -191,13 +197,15 @@ size_t exl3_argmax_scratch_bytes(int R, int V);
 // Whole prompts on tcgen05 tensor cores with TMA loads from the paged cache (bfloat16, heads of 64 or 128, pages
 // of 64, tiles of 128 queries); variant 0: chosen by the number of blocks, 1: a tile a block, 2: four blocks an SM
 // (heads of 64), 3: two tiles a block (the first of the list with the last, and so on); see attention_prefill_tc.cu.
+// chunk > 0: a query also sees nothing before its own block of chunk positions; sink != 0: one more in the softmax's
+// denominator (both as in exl3_attn_tokens_ex; the decode kernel below takes the same two).
 int exl3_attn_prefill_tc_supported(int dtype, int hd, int page);
 int exl3_attn_prefill_tc_status();
 int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, void* out, const void* k_pool,
                          const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
                          const int* row_start, const int* row_pos0, const int* tile_seq, const int* tile_q0,
-                         int n_tiles, int nh, int nkv, int hd, int page, int window, float scale, int variant,
-                         cudaStream_t stream);
+                         int n_tiles, int nh, int nkv, int hd, int page, int window, int chunk, int sink, float scale,
+                         int variant, cudaStream_t stream);
 
 // exl3_gemv_bf16 as the two sides of a norm that is no kernel of its own.  With ss_in the input is the x_raw of a
 // producing call and the results are multiplied by rsqrt(sum of ss_in's blocks / width + eps) per batch row.
@@ -253,8 +261,8 @@ int exl3_attn_decode_supported(int dtype, int T, int nh, int nkv, int hd, int pa
 int exl3_attn_decode_status();
 int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_pool, void* v_pool,
                      int64_t n_pool_rows, const int* block_table, int bt_stride, const int* tok_pos,
-                     const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window, float scale,
-                     int split_keys, int max_splits, float* scratch, size_t scratch_bytes, const float* inv_freq,
+                     const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window, int chunk, int sink,
+                     float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes, const float* inv_freq,
                      const float* inv_freq_lo, int rot, float pos_scale, int write_new, int head_split, int in_block,
                      int twins, cudaStream_t stream);
 

@@ -187,7 +187,8 @@ __global__ void __launch_bounds__((TW + 1) * AD_WARPS * 32, 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, __nv_bfloat16* __restrict__ out,
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
-                   const int* __restrict__ tok_seq, int T, int nh, int nkv, int window, float scale_log2,
+                   const int* __restrict__ tok_seq, int T, int nh, int nkv, int window, int chunk, int sink,
+                   float scale_log2,
                    int split_keys, int max_splits, float* __restrict__ scratch, int* __restrict__ counters,
                    const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo, float pos_scale,
                    int rotate, int write_new,
@@ -240,7 +241,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   // ---- every token's chunks, counted and summed ------------------------------------------------
   // A token at position pos reads keys lo .. pos; its chunks are the aligned pieces of split_keys
   // keys that this range touches, numbered from 0.
-  auto first_key = [&](int pos) { return (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0; };
+  // chunk > 0: nothing before the token's own block of chunk positions either
+  auto first_key = [&](int pos) {
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    return chunk > 0 ? max(lo, pos / chunk * chunk) : lo;
+  };
   for (int i = threadIdx.x; i < T; i += blockDim.x) {
     const int pos = __ldcg(tok_pos + i);
     s_pos[i] = pos;
@@ -516,6 +521,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
           ll += lv[n * n_rec + s2] * w;
         }
         ll = warp_sum(ll);
+        if (sink) ll += ad_exp2(-M);
         if (nn == n) my_ll = ll;
       }
     }
@@ -789,7 +795,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         const int head = g * G + n;
         if (n_rec == 1) {
           __nv_bfloat16* dst = out + ((int64_t)t * nh + head) * HD;
-          const float inv = 1.0f / l[c][h];
+          // a sink is one more key of score 0 without a value: a term exp2(0 - m) in the sum
+          const float inv = 1.0f / (sink ? l[c][h] + ad_exp2(-m[c][h]) : l[c][h]);
 #pragma unroll
           for (int d = 0; d < NJ; ++d) {
             dst[16 * d + gl] = __float2bfloat16(o[c][d][h] * inv);
@@ -853,6 +860,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
           w[s2] = s2 < n_rec ? ad_exp2(rec_at(hb, s2, HD) - M) : 0.0f;
           ll += s2 < n_rec ? rec_at(hb, s2, HD + 1) * w[s2] : 0.0f;
         }
+        if (sink) ll += ad_exp2(-M);
         __nv_bfloat16* dst = out + ((int64_t)t_blk * nh + g_blk * G + n) * HD;
 #pragma unroll
         for (int e = 0; e < HD / 32; ++e) {
@@ -957,7 +965,8 @@ extern "C" int exl3_attn_decode_status() {
 // queries and the new key; rot = 0: none.
 extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_pool, void* v_pool,
                                 int64_t n_pool_rows, const int* block_table, int bt_stride, const int* tok_pos,
-                                const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window,
+                                const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window, int chunk,
+                                int sink,
                                 float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
                                 const float* inv_freq, const float* inv_freq_lo, int rot, float pos_scale,
                                 int write_new, int head_split, int in_block, int twins, cudaStream_t stream) {
@@ -1040,7 +1049,7 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
              in_block == 2 ? 2u : 1u,                                                                              \
              (size_t)AD_SMEM, stream, map_k, map_v,                                                                \
              static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,  \
-             bt_stride, tok_pos, tok_seq, T, nh, groups, window, scale * 1.4426950408889634f, split_keys,        \
+             bt_stride, tok_pos, tok_seq, T, nh, groups, window, chunk, sink, scale * 1.4426950408889634f, split_keys,        \
              max_splits, records, counters, inv_freq, inv_freq_lo, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,            \
              static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), head_split, in_block)
   const bool wide = nh / groups > 8;                       // more than one block of 8 query heads per group

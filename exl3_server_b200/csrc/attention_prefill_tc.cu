@@ -182,7 +182,8 @@ struct FaTile {
   const int* bt;   // the sequence's page table
 };
 __device__ inline FaTile fa_tile(int tile, const int* block_table, int bt_stride, const int* row_start,
-                                 const int* row_pos0, const int* tile_seq, const int* tile_q0, int window) {
+                                 const int* row_pos0, const int* tile_seq, const int* tile_q0, int window,
+                                 int chunk) {
   FaTile t;
   const int b = tile_seq[tile], q0 = tile_q0[tile];
   const int n_new = row_start[b + 1] - row_start[b];
@@ -190,7 +191,8 @@ __device__ inline FaTile fa_tile(int tile, const int* block_table, int bt_stride
   t.rows = min(FA_BQ, n_new - q0);
   t.p_first = row_pos0[b] + q0;
   t.p_last = t.p_first + t.rows - 1;
-  const int k_lo = (window > 0 && t.p_first - window + 1 > 0) ? t.p_first - window + 1 : 0;
+  int k_lo = (window > 0 && t.p_first - window + 1 > 0) ? t.p_first - window + 1 : 0;
+  if (chunk > 0) k_lo = max(k_lo, t.p_first / chunk * chunk);    // the block of positions of the tile's first query
   t.page_lo = k_lo / FA_BK;
   t.n_pages = t.p_last / FA_BK - t.page_lo + 1;
   t.bt = block_table + (int64_t)b * bt_stride;
@@ -208,7 +210,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
                        const int* __restrict__ row_pos0, const int* __restrict__ tile_seq,
                        const int* __restrict__ tile_q0, int n_tiles, int fold, int nh, int nkv, int window,
-                       float scale_log2) {
+                       int chunk, int sink, float scale_log2) {
   extern __shared__ unsigned char fa_smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr int NB = FA_HD / 64;                             // boxes of 64 features (128-byte lines) in a head
@@ -234,7 +236,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int other = n_tiles - 1 - (int)blockIdx.y;
   const int n_own = (fold && other > (int)blockIdx.y) ? 2 : 1;
   auto tile_of = [&](int w) {                       // the block's first (w = 0) or second tile
-    return fa_tile(w ? other : (int)blockIdx.y, block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, window);
+    return fa_tile(w ? other : (int)blockIdx.y, block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, window, chunk);
   };
 
   if (threadIdx.x == 0) {
@@ -404,12 +406,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const bool p_free = f < 2 || fa_mbar_test(pv_done + st, ((f - 2) >> 1) & 1);
       const bool s_there = j + 1 < n_blocks && fa_mbar_test(s_full + (st ^ 1), ((f + 1) >> 1) & 1);
       const int key0 = (page_lo + j) * FA_BK;
-      const bool need_mask = (key0 + FA_BK - 1 > p_first) || (window > 0 && key0 <= p_last - window);
+      const bool need_mask = (key0 + FA_BK - 1 > p_first) || (window > 0 && key0 <= p_last - window) ||
+                             (chunk > 0 && key0 < p_last / chunk * chunk);
       // four independent chains for the maximum (and below for the sum): the row is long and
       // a single chain would make every step wait for the one before
       // masking without branches (one test per page decides whether the page needs it at all)
       if (need_mask) {
-        const int lo_key = (window > 0) ? p - window : -1;    // keys <= lo_key are out of the window
+        int lo_key = (window > 0) ? p - window : -1;          // keys <= lo_key are out of the window
+        if (chunk > 0) lo_key = max(lo_key, p / chunk * chunk - 1);   // or before the query's block of positions
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -481,7 +485,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       ok = fa_mbar_wait(pv_done + (fl & 1), (fl >> 1) & 1);
       if (ok) {
         fa_fence_after();
-        const float inv = 1.0f / l_run;
+        // a sink is a key of score 0 without a value: one more term in the sum, in the units of the reference maximum
+        const float inv = 1.0f / (sink ? l_run + fa_exp2(-m_used) : l_run);
         __nv_bfloat16* dst = out + ((int64_t)(tw.row0 + r) * nh + head) * FA_HD;
 #pragma unroll
         for (int h2 = 0; h2 < FA_HD / 64; ++h2) {            // 64 columns at a time (every thread reads: the load is the warp's)
@@ -537,7 +542,8 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
                         const int* __restrict__ row_pos0, const int* __restrict__ tile_seq,
-                        const int* __restrict__ tile_q0, int nh, int nkv, int window, float scale_log2) {
+                        const int* __restrict__ tile_q0, int nh, int nkv, int window, int chunk, int sink,
+                        float scale_log2) {
   extern __shared__ unsigned char fa_smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr uint32_t QB = fa_q_bytes(64), KVB = fa_kv_bytes(64);
@@ -561,7 +567,8 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int g = head / (nh / nkv);
   const int rows = min(FA_BQ, n_new - q0);
   const int p_first = pos0 + q0, p_last = pos0 + q0 + rows - 1;
-  const int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  if (chunk > 0) k_lo = max(k_lo, p_first / chunk * chunk);
   const int page_lo = k_lo / FA_BK, page_hi = p_last / FA_BK;
   const int n_blocks = page_hi - page_lo + 1;
   const int* bt = block_table + (int64_t)b * bt_stride;
@@ -651,9 +658,11 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       fa_ld32(tmem_base + lane_addr + 32, sr[1]);
       fa_wait_ld();
       const int key0 = (page_lo + j) * FA_BK;
-      const bool need_mask = (key0 + FA_BK - 1 > p_first) || (window > 0 && key0 <= p_last - window);
+      const bool need_mask = (key0 + FA_BK - 1 > p_first) || (window > 0 && key0 <= p_last - window) ||
+                             (chunk > 0 && key0 < p_last / chunk * chunk);
       if (need_mask) {
-        const int lo_key = (window > 0) ? p - window : -1;
+        int lo_key = (window > 0) ? p - window : -1;
+        if (chunk > 0) lo_key = max(lo_key, p / chunk * chunk - 1);
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -716,7 +725,7 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ok = fa_mbar_wait(pv_done, jl & 1);
       if (ok) {
         fa_fence_after();
-        const float inv = 1.0f / l_run;
+        const float inv = 1.0f / (sink ? l_run + fa_exp2(-m_used) : l_run);
         __nv_bfloat16* dst = out + ((int64_t)(row_start[b] + q0 + r) * nh + head) * 64;
 #pragma unroll 1
         for (int c0 = 0; c0 < 64; c0 += 32) {
@@ -799,7 +808,7 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
                                     const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
                                     const int* row_start, const int* row_pos0, const int* tile_seq,
                                     const int* tile_q0, int n_tiles, int nh, int nkv, int hd, int page, int window,
-                                    float scale, int variant, cudaStream_t stream) {
+                                    int chunk, int sink, float scale, int variant, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   if (!exl3_attn_prefill_tc_supported(DT_BF16, hd, page)) {
     set_error("attn_prefill_tc: needs bfloat16, head_dim 64 or 128 and pages of 64, got head_dim %d page %d", hd, page);
@@ -809,7 +818,7 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
     set_error("attn_prefill_tc: variant is 0 (chosen), 1 (a tile a block), 2 (four blocks an SM, heads of 64) or 3 (two tiles a block), got %d", variant);
     return ERR_BAD_ARGUMENT;
   }
-  if (n_tiles < 0 || T < 1 || nh < 1 || nkv < 1 || nh % nkv != 0 || n_tiles > 65535 || window < 0 || q_row_stride % 8 != 0) {
+  if (n_tiles < 0 || T < 1 || nh < 1 || nkv < 1 || nh % nkv != 0 || n_tiles > 65535 || window < 0 || chunk < 0 || q_row_stride % 8 != 0) {
     set_error("attn_prefill_tc: bad sizes tiles=%d T=%d heads=%d kv_heads=%d window=%d", n_tiles, T, nh, nkv, window);
     return ERR_BAD_ARGUMENT;
   }
@@ -850,12 +859,12 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
   const float scale_log2 = scale * 1.4426950408889634f;
   if (four)
     launch_pdl(attn_prefill_tc4_kernel, grid, dim3(FA_THREADS), F4_SMEM, stream, map_q, map_k, map_v, o, block_table,
-               bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, scale_log2);
+               bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, chunk, sink, scale_log2);
   else if (hd == 64)
     launch_pdl(attn_prefill_tc_kernel<64>, grid, dim3(FA_THREADS_MAIN), fa_smem(64), stream, map_q, map_k, map_v, o,
-               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, n_tiles, fold, nh, nkv, window, scale_log2);
+               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, n_tiles, fold, nh, nkv, window, chunk, sink, scale_log2);
   else
     launch_pdl(attn_prefill_tc_kernel<128>, grid, dim3(FA_THREADS_MAIN), fa_smem(128), stream, map_q, map_k, map_v, o,
-               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, n_tiles, fold, nh, nkv, window, scale_log2);
+               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, n_tiles, fold, nh, nkv, window, chunk, sink, scale_log2);
   return launch_status("attn_prefill_tc");
 }

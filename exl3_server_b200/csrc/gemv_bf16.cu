@@ -32,8 +32,23 @@ extern "C" int exl3_gemv_bf16(const void* x, const void* w, const void* bias, vo
 
 // The plain projection with the xIELU activation on its results (EPI 3 in gemv_bf16.cuh): act_p = softplus(p),
 // act_n = 1/2 + softplus(q).
+static int gemv_act(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N, int K,
+                    float act_p, float act_n, int act_kind, cudaStream_t stream);
+
 extern "C" int exl3_gemv_bf16_act(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M,
                                   int N, int K, float act_p, float act_n, cudaStream_t stream) {
+  return gemv_act(x, w, bias, y, out_dtype, M, N, K, act_p, act_n, 0, stream);
+}
+
+// The same with GELU on the results: kind 0 exact (erf), 1 by the tanh formula.
+extern "C" int exl3_gemv_bf16_gelu(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M,
+                                   int N, int K, int kind, cudaStream_t stream) {
+  if (kind < 0 || kind > 1) { set_error("gemv_bf16_gelu: kind is 0 (erf) or 1 (tanh)"); return ERR_BAD_ARGUMENT; }
+  return gemv_act(x, w, bias, y, out_dtype, M, N, K, 0.0f, 0.0f, 1 + kind, stream);
+}
+
+static int gemv_act(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N, int K,
+                    float act_p, float act_n, int act_kind, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (M < 0 || M > 16 || N < 0 || K < 8 || K % 8 != 0) {
     set_error("gemv_bf16_act: needs 1 <= M <= 16 and K a multiple of 8, got M=%d N=%d K=%d", M, N, K);
@@ -45,6 +60,7 @@ extern "C" int exl3_gemv_bf16_act(const void* x, const void* w, const void* bias
   GemvNorm nrm = {};
   nrm.act_p = act_p;
   nrm.act_n = act_n;
+  nrm.act_kind = act_kind;
   int warps, stages;
   const int nt = gemv_shape(M, N, K, warps, stages);
   if (nt == 1)

@@ -72,9 +72,17 @@ struct GemvNorm {
   const float* ss_in;            // [16, ss_blocks] from the producer
   int ss_blocks;
   float eps, width;
-  // EPI 3: the two constants of the activation applied to the results (see below)
+  // EPI 3: the activation applied to the results: act_kind 0 xIELU with its two constants (see below), 1 the exact
+  // GELU z/2 (1 + erf(z / sqrt 2)), 2 GELU by the tanh formula
   float act_p, act_n;
+  int act_kind;
 };
+
+__device__ inline float gemv_activation(float s, float act_p, float act_n, int kind) {
+  if (kind == 1) return 0.5f * s * (1.0f + erff(s * 0.70710678118654752f));
+  if (kind == 2) return 0.5f * s * (1.0f + tanhf(0.79788456080286536f * (s + 0.044715f * s * s * s)));
+  return s > 0.0f ? fmaf(act_p * s, s, 0.5f * s) : fmaf(act_n, expm1f(s) - s, 0.5f * s);
+}
 
 // EPI 0: y[m, n] = acc (+ bias).  EPI 3: the same through the xIELU activation, a(z) = act_p z^2 + z / 2 for z > 0 and
 // act_n (exp(z) - 1 - z) + z / 2 otherwise (act_p = softplus(p), act_n = 1/2 + softplus(q), worked out by the caller).
@@ -223,7 +231,7 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
       for (int wi = 0; wi < nwarps; ++wi) s += part[wi][r][m];
       if (SCALE) s *= s_inv[m];
       if (bias) s += __bfloat162float(bias[n]);
-      if (EPI == 3) s = s > 0.0f ? fmaf(nrm.act_p * s, s, 0.5f * s) : fmaf(nrm.act_n, expm1f(s) - s, 0.5f * s);
+      if (EPI == 3) s = gemv_activation(s, nrm.act_p, nrm.act_n, nrm.act_kind);
       Elem<TO>::store(y + (int64_t)m * N + n, s);
     }
   } else if (EPI == 1) {

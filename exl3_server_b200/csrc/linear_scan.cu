@@ -67,6 +67,55 @@ token_shift_kernel(const void* h, int h_dtype, const void* __restrict__ mu, int 
   }
 }
 
+// Eight consecutive values as floats from float32 or bfloat16 storage, through L2; and back.
+__device__ inline void ls_load8(const float* p, float (&v)[8]) {
+  float a[4], b[4];
+  load_vec_cg(p, a);
+  load_vec_cg(p + 4, b);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { v[e] = a[e]; v[4 + e] = b[e]; }
+}
+__device__ inline void ls_load8(const __nv_bfloat16* p, float (&v)[8]) { load_vec_cg(p, v); }
+__device__ inline void ls_store8(float* p, const float (&v)[8]) {
+  const float a[4] = {v[0], v[1], v[2], v[3]}, b[4] = {v[4], v[5], v[6], v[7]};
+  store_vec(p, a);
+  store_vec(p + 4, b);
+}
+__device__ inline void ls_store8(__nv_bfloat16* p, const float (&v)[8]) { store_vec(p, v); }
+
+// Token shift with eight features a thread (H a multiple of 8, float32 mu).
+template <typename TH, typename TO>
+__global__ void __launch_bounds__(256)
+token_shift_vec_kernel(const TH* h, const float* __restrict__ mu, int n_mix, float* prev, const int* __restrict__ tok_seq,
+                       const int* __restrict__ row_start, const int* __restrict__ slot_ids, TO* out, int T, int H) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int b = __ldcg(tok_seq + t);
+  const int first = __ldcg(row_start + b), end = __ldcg(row_start + b + 1);
+  float* st = prev + (int64_t)__ldcg(slot_ids + b) * H;
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float x[8], before[8];
+    ls_load8(h + (int64_t)t * H + c, x);
+    if (t == first) {
+      float last[8];
+      ls_load8(st + c, before);
+      ls_load8(h + (int64_t)(end - 1) * H + c, last);
+      ls_store8(st + c, last);
+    } else {
+      ls_load8(h + (int64_t)(t - 1) * H + c, before);
+    }
+    for (int s = 0; s < n_mix; ++s) {
+      float m[8], o[8];
+      load_vec(mu + (int64_t)s * H + c, reinterpret_cast<float(&)[4]>(m[0]));
+      load_vec(mu + (int64_t)s * H + c + 4, reinterpret_cast<float(&)[4]>(m[4]));
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = fmaf(before[e] - x[e], m[e], x[e]);
+      ls_store8(out + ((int64_t)s * T + t) * H + c, o);
+    }
+  }
+}
+
 // ---- the scan ------------------------------------------------------------------------------------------------------
 
 constexpr int LS_STAGE = 8;                      // tokens staged in shared memory at a time
@@ -211,6 +260,149 @@ __global__ void linear_scan_kernel(ScanArgs a, int phase) {
   }
 }
 
+// The same with a thread's column of S in registers, for key sizes of 16, 32, 64 and 128 and up to 256 values a
+// head: no shared-memory traffic for the state, and r, k and the decays read four at a time.  (With the state in
+// shared memory a token costs a warp five shared-memory instructions per key channel, which is what bounded the
+// kernel: 8,192 tokens of 32 heads of 64 x 64 took 0.94 ms a launch.)
+template <int MODE, int DK>
+__global__ void __launch_bounds__(256) linear_scan_reg_kernel(ScanArgs a, int phase) {
+  __shared__ __align__(16) float sr[LS_STAGE * DK];
+  __shared__ __align__(16) float sk[LS_STAGE * DK];
+  __shared__ __align__(16) float sw[MODE == 0 ? LS_STAGE * DK : 4];
+  __shared__ float sb[LS_STAGE];
+  __shared__ float sA[DK];
+  const int dv = a.dv;
+  pdl_wait();
+  pdl_trigger();
+  const int hd = blockIdx.x, c = blockIdx.y, b = blockIdx.z;
+  const int t0 = __ldcg(a.row_start + b), t1 = __ldcg(a.row_start + b + 1);
+  int lo = t0, hi = t1;
+  if (phase == 1) {
+    lo = t0 + c * LS_CHUNK;
+    hi = lo + LS_CHUNK;
+    if (hi >= t1) return;
+  } else if (phase == 2) {
+    lo = t0 + c * LS_CHUNK;
+    hi = min(lo + LS_CHUNK, t1);
+    if (lo >= t1) return;
+  }
+  const int j = threadIdx.x;
+  const bool col = j < dv;
+  float* st = a.state + ((int64_t)__ldcg(a.slot_ids + b) * a.heads + hd) * DK * dv;
+  const int64_t rec = (int64_t)DK + (int64_t)DK * dv;
+  float* snap = a.snap + ((int64_t)b * a.heads + hd) * DK * dv;
+  float S[DK];
+  if (phase == 1) {
+#pragma unroll
+    for (int i = 0; i < DK; ++i) S[i] = 0.0f;
+    for (int i = j; i < DK; i += blockDim.x) sA[i] = 1.0f;
+    if (c == 0 && col) {
+#pragma unroll
+      for (int i = 0; i < DK; ++i) snap[i * dv + j] = __ldcg(st + i * dv + j);
+    }
+  } else {
+    const float* from = (phase == 2 && t1 - t0 > LS_CHUNK) ? snap : st;
+#pragma unroll
+    for (int i = 0; i < DK; ++i) S[i] = col ? __ldcg(from + i * dv + j) : 0.0f;
+    if (phase == 2 && col) {
+      for (int p = 0; p < c; ++p) {
+        const float* ab = a.ab + ((int64_t)ls_place(t0, b, p) * a.heads + hd) * rec;
+#pragma unroll
+        for (int i = 0; i < DK; ++i) S[i] = fmaf(__ldcg(ab + i), S[i], __ldcg(ab + DK + i * dv + j));
+      }
+    }
+  }
+  const float gamma = MODE == 1 ? a.decay[hd] : 0.0f;
+  for (int s0 = lo; s0 < hi; s0 += LS_STAGE) {
+    const int n = min(LS_STAGE, hi - s0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n * DK; idx += blockDim.x) {
+      const int tt = idx / DK, i = idx - tt * DK;
+      const int64_t t = s0 + tt;
+      sr[idx] = ls_load_act(a.r, a.rk_dtype, t * a.r_ld + (int64_t)hd * DK + i);
+      sk[idx] = ls_load_act(a.k, a.rk_dtype, t * a.k_ld + (int64_t)hd * DK + i);
+      if (MODE == 0) {
+        const float z = ls_load_act(a.wraw, a.w_dtype, t * a.w_ld + (int64_t)hd * DK + i) +
+                        ls_load(a.w0, a.wu_dtype, (int64_t)hd * DK + i);
+        sw[idx] = expf(-expf(z));
+      }
+    }
+    __syncthreads();
+    if (MODE == 0) {
+      const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+      for (int tt = warp; tt < n; tt += nw) {
+        float acc = 0.0f;
+        for (int i = lane; i < DK; i += 32)
+          acc = fmaf(sr[tt * DK + i] * ls_load(a.u, a.wu_dtype, (int64_t)hd * DK + i), sk[tt * DK + i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) sb[tt] = acc;
+      }
+      if (phase == 1)
+        for (int i = threadIdx.x; i < DK; i += blockDim.x) {
+          float p = sA[i];
+          for (int tt = 0; tt < n; ++tt) p *= sw[tt * DK + i];
+          sA[i] = p;
+        }
+      __syncthreads();
+    } else if (phase == 1) {
+      for (int i = threadIdx.x; i < DK; i += blockDim.x) {
+        float p = sA[i];
+        for (int tt = 0; tt < n; ++tt) p *= gamma;
+        sA[i] = p;
+      }
+    }
+    if (col) {
+      // the values of the stage's tokens, asked for together
+      float vj[LS_STAGE];
+#pragma unroll
+      for (int tt = 0; tt < LS_STAGE; ++tt)
+        vj[tt] = tt < n ? ls_load_act(a.v, a.v_dtype, (int64_t)(s0 + tt) * a.v_ld + (int64_t)hd * dv + j) : 0.0f;
+#pragma unroll
+      for (int tt = 0; tt < LS_STAGE; ++tt) {
+        if (tt < n) {
+          const float4* rr = reinterpret_cast<const float4*>(sr + tt * DK);
+          const float4* kk = reinterpret_cast<const float4*>(sk + tt * DK);
+          float acc = 0.0f;
+          if (MODE == 0) {
+            const float4* ww = reinterpret_cast<const float4*>(sw + tt * DK);
+#pragma unroll
+            for (int i4 = 0; i4 < DK / 4; ++i4) {
+              const float4 r4 = rr[i4], k4 = kk[i4], w4 = ww[i4];
+              acc = fmaf(r4.x, S[4 * i4 + 0], acc); S[4 * i4 + 0] = fmaf(w4.x, S[4 * i4 + 0], k4.x * vj[tt]);
+              acc = fmaf(r4.y, S[4 * i4 + 1], acc); S[4 * i4 + 1] = fmaf(w4.y, S[4 * i4 + 1], k4.y * vj[tt]);
+              acc = fmaf(r4.z, S[4 * i4 + 2], acc); S[4 * i4 + 2] = fmaf(w4.z, S[4 * i4 + 2], k4.z * vj[tt]);
+              acc = fmaf(r4.w, S[4 * i4 + 3], acc); S[4 * i4 + 3] = fmaf(w4.w, S[4 * i4 + 3], k4.w * vj[tt]);
+            }
+            acc = fmaf(sb[tt], vj[tt], acc);
+          } else {
+#pragma unroll
+            for (int i4 = 0; i4 < DK / 4; ++i4) {
+              const float4 r4 = rr[i4], k4 = kk[i4];
+              S[4 * i4 + 0] = fmaf(gamma, S[4 * i4 + 0], k4.x * vj[tt]); acc = fmaf(r4.x, S[4 * i4 + 0], acc);
+              S[4 * i4 + 1] = fmaf(gamma, S[4 * i4 + 1], k4.y * vj[tt]); acc = fmaf(r4.y, S[4 * i4 + 1], acc);
+              S[4 * i4 + 2] = fmaf(gamma, S[4 * i4 + 2], k4.z * vj[tt]); acc = fmaf(r4.z, S[4 * i4 + 2], acc);
+              S[4 * i4 + 3] = fmaf(gamma, S[4 * i4 + 3], k4.w * vj[tt]); acc = fmaf(r4.w, S[4 * i4 + 3], acc);
+            }
+          }
+          if (phase != 1) a.out[(int64_t)(s0 + tt) * ((int64_t)a.heads * dv) + (int64_t)hd * dv + j] = acc;
+        }
+      }
+    }
+  }
+  if (phase == 1) {
+    __syncthreads();
+    float* ab = a.ab + ((int64_t)ls_place(t0, b, c) * a.heads + hd) * rec;
+    for (int i = threadIdx.x; i < DK; i += blockDim.x) ab[i] = sA[i];
+    if (col) {
+#pragma unroll
+      for (int i = 0; i < DK; ++i) ab[DK + i * dv + j] = S[i];
+    }
+  } else if (hi == t1 && col) {
+#pragma unroll
+    for (int i = 0; i < DK; ++i) st[i * dv + j] = S[i];
+  }
+}
+
 // ---- per-head norm and gate ------------------------------------------------------------------------------------------
 
 __global__ void __launch_bounds__(128)
@@ -241,6 +433,40 @@ head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, c
   }
 }
 
+// The same with four values a lane (dv a multiple of 4, at most 128 a head: one piece a lane), float32 weight.
+template <typename TG, typename TO>
+__global__ void __launch_bounds__(128)
+head_norm_gate_vec_kernel(const float* o, const float* __restrict__ w, const TG* gate, int64_t gate_ld, float eps,
+                          TO* out, int n_items, int heads, int dv) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= n_items) return;
+  const int t = item / heads, hd = item - t * heads;
+  const int e = lane * 4;
+  float x[4] = {0.0f, 0.0f, 0.0f, 0.0f}, g[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (e < dv) {
+    load_vec_cg(o + (int64_t)item * dv + e, x);
+    if (gate) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)                                      // through L2: a kernel of this step wrote it
+        g[i] = ls_load_act(gate, Elem<TG>::code, (int64_t)t * gate_ld + (int64_t)hd * dv + e + i);
+    }
+  }
+  const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+  const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+  if (e < dv) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float v = x[i] * inv;
+      if (w) v *= w[(int64_t)hd * dv + e + i];
+      if (gate) v *= g[i] / (1.0f + __expf(-g[i]));
+      Elem<TO>::store(out + (int64_t)item * dv + e + i, v);
+    }
+  }
+}
+
 }  // namespace exl3
 
 using namespace exl3;
@@ -261,8 +487,19 @@ extern "C" int exl3_token_shift(const void* h, int h_dtype, const void* mu, int 
     set_error("token_shift: bad sizes T=%d H=%d mixes=%d", T, H, n_mix);
     return ERR_BAD_ARGUMENT;
   }
-  launch_pdl(token_shift_kernel, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream, h, h_dtype, mu, mu_dtype, n_mix,
-             prev, tok_seq, row_start, slot_ids, out, out_dtype, T, H);
+  const bool vec = H % 8 == 0 && mu_dtype == DT_F32 && h_dtype == out_dtype && aligned16(h) && aligned16(mu) &&
+                   aligned16(prev) && aligned16(out);
+  const dim3 threads(H >= 2048 ? 256 : 128);
+  if (vec && h_dtype == DT_BF16)
+    launch_pdl(token_shift_vec_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), threads, 0, stream,
+               static_cast<const __nv_bfloat16*>(h), static_cast<const float*>(mu), n_mix, prev, tok_seq, row_start,
+               slot_ids, static_cast<__nv_bfloat16*>(out), T, H);
+  else if (vec && h_dtype == DT_F32)
+    launch_pdl(token_shift_vec_kernel<float, float>, dim3(T), threads, 0, stream, static_cast<const float*>(h),
+               static_cast<const float*>(mu), n_mix, prev, tok_seq, row_start, slot_ids, static_cast<float*>(out), T, H);
+  else
+    launch_pdl(token_shift_kernel, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream, h, h_dtype, mu, mu_dtype, n_mix,
+               prev, tok_seq, row_start, slot_ids, out, out_dtype, T, H);
   return launch_status("token_shift");
 }
 
@@ -277,12 +514,24 @@ extern "C" int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const voi
     set_error("linear_scan: bad arguments mode=%d rows=%d tokens=%d heads=%d dk=%d dv=%d", mode, B, T, heads, dk, dv);
     return ERR_BAD_ARGUMENT;
   }
-  const size_t smem = ((size_t)dk * dv + 3 * (size_t)LS_STAGE * dk + LS_STAGE + dk) * sizeof(float);
+  size_t smem = ((size_t)dk * dv + 3 * (size_t)LS_STAGE * dk + LS_STAGE + dk) * sizeof(float);
   if (smem > 200 * 1024) {
     set_error("linear_scan: a state of %d x %d per head does not fit shared memory", dk, dv);
     return ERR_UNSUPPORTED;
   }
-  auto kernel = mode == 0 ? linear_scan_kernel<0> : linear_scan_kernel<1>;
+  void (*kernel)(ScanArgs, int) = mode == 0 ? linear_scan_kernel<0> : linear_scan_kernel<1>;
+  // key sizes of 16, 32, 64 and 128 with up to 256 values a head: the state in registers
+  bool regs = dv <= 256;
+  if (regs) {
+    switch (dk) {
+      case 16: kernel = mode == 0 ? linear_scan_reg_kernel<0, 16> : linear_scan_reg_kernel<1, 16>; break;
+      case 32: kernel = mode == 0 ? linear_scan_reg_kernel<0, 32> : linear_scan_reg_kernel<1, 32>; break;
+      case 64: kernel = mode == 0 ? linear_scan_reg_kernel<0, 64> : linear_scan_reg_kernel<1, 64>; break;
+      case 128: kernel = mode == 0 ? linear_scan_reg_kernel<0, 128> : linear_scan_reg_kernel<1, 128>; break;
+      default: regs = false;
+    }
+  }
+  if (regs) smem = 0;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
@@ -320,7 +569,21 @@ extern "C" int exl3_head_norm_gate(const float* o, const void* w, int w_dtype, c
   if (T == 0) return 0;
   if (T < 0 || heads < 1 || dv < 1) { set_error("head_norm_gate: bad sizes"); return ERR_BAD_ARGUMENT; }
   const int items = T * heads;
-  launch_pdl(head_norm_gate_kernel, dim3(ceil_div(items, 4)), dim3(128), 0, stream, o, w, w_dtype, gate, gate_dtype,
-             gate_ld, eps, out, out_dtype, items, heads, dv);
+  const bool vec = dv % 4 == 0 && dv <= 128 && (w == nullptr || w_dtype == DT_F32) && aligned16(o) &&
+                   (gate == nullptr || gate_ld % 4 == 0);
+  const float* wf = static_cast<const float*>(w);
+  const dim3 grid(ceil_div(items, 4)), threads(128);
+  if (vec && gate_dtype == DT_BF16 && out_dtype == DT_BF16)
+    launch_pdl(head_norm_gate_vec_kernel<__nv_bfloat16, __nv_bfloat16>, grid, threads, 0, stream, o, wf,
+               static_cast<const __nv_bfloat16*>(gate), gate_ld, eps, static_cast<__nv_bfloat16*>(out), items, heads, dv);
+  else if (vec && gate_dtype == DT_F32 && out_dtype == DT_BF16)
+    launch_pdl(head_norm_gate_vec_kernel<float, __nv_bfloat16>, grid, threads, 0, stream, o, wf,
+               static_cast<const float*>(gate), gate_ld, eps, static_cast<__nv_bfloat16*>(out), items, heads, dv);
+  else if (vec && gate_dtype == DT_F32 && out_dtype == DT_F32)
+    launch_pdl(head_norm_gate_vec_kernel<float, float>, grid, threads, 0, stream, o, wf, static_cast<const float*>(gate),
+               gate_ld, eps, static_cast<float*>(out), items, heads, dv);
+  else
+    launch_pdl(head_norm_gate_kernel, grid, threads, 0, stream, o, w, w_dtype, gate, gate_dtype, gate_ld, eps, out,
+               out_dtype, items, heads, dv);
   return launch_status("head_norm_gate");
 }

@@ -180,6 +180,150 @@ static void norm_add_vec(float* h, const void* y, const void* w, float eps, void
                static_cast<const TY*>(y), static_cast<const TW*>(w), eps, static_cast<__nv_bfloat16*>(x), H);
 }
 
+// norm_add followed by the next sublayer's input norm over the new residual, in one pass: a thread keeps its
+// values of the row in registers between the two (rows up to NA_KEEP * NA_THREADS values; beyond that the rest is
+// read again).
+__global__ void __launch_bounds__(NA_THREADS)
+norm_add_norm_kernel(float* h, const void* y, int y_dtype, const void* __restrict__ w, int w_dtype, float eps,
+                     const void* __restrict__ w2, int w2_dtype, float eps2, void* x, int x_dtype, int H) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int64_t base = (int64_t)blockIdx.x * H;
+  float keep[NA_KEEP];
+  float ss = 0.0f;
+#pragma unroll
+  for (int p = 0; p < NA_KEEP; ++p) {
+    const int c = p * NA_THREADS + threadIdx.x;
+    keep[p] = c < H ? on_load_act(y, y_dtype, base + c) : 0.0f;
+    ss += keep[p] * keep[p];
+  }
+  for (int c = NA_KEEP * NA_THREADS + threadIdx.x; c < H; c += NA_THREADS) {
+    const float v = on_load_act(y, y_dtype, base + c);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  float ss2 = 0.0f;
+#pragma unroll
+  for (int p = 0; p < NA_KEEP; ++p) {
+    const int c = p * NA_THREADS + threadIdx.x;
+    if (c < H) {
+      const float v = __ldcg(h + base + c) + keep[p] * inv * on_load_any(w, w_dtype, c);
+      h[base + c] = v;
+      keep[p] = v;
+      ss2 += v * v;
+    }
+  }
+  for (int c = NA_KEEP * NA_THREADS + threadIdx.x; c < H; c += NA_THREADS) {
+    const float v = __ldcg(h + base + c) + on_load_act(y, y_dtype, base + c) * inv * on_load_any(w, w_dtype, c);
+    h[base + c] = v;
+    ss2 += v * v;
+  }
+  ss2 = block_sum(ss2, red);
+  const float inv2 = 1.0f / sqrtf(ss2 / (float)H + eps2);
+#pragma unroll
+  for (int p = 0; p < NA_KEEP; ++p) {
+    const int c = p * NA_THREADS + threadIdx.x;
+    if (c < H) on_store_any(x, x_dtype, base + c, keep[p] * inv2 * on_load_any(w2, w2_dtype, c));
+  }
+  for (int c = NA_KEEP * NA_THREADS + threadIdx.x; c < H; c += NA_THREADS)      // the same thread wrote h[c]
+    on_store_any(x, x_dtype, base + c, h[base + c] * inv2 * on_load_any(w2, w2_dtype, c));
+}
+
+// The same for rows of up to NA_THREADS * 8 * NA_VECS values, a multiple of 8, with float32 weights: a thread keeps its
+// pieces of the row in registers through both norms and every access is 16 or 32 bytes wide.
+template <typename TY, typename TX>
+__global__ void __launch_bounds__(NA_THREADS)
+norm_add_norm_vec_kernel(float* h, const TY* y, const float* __restrict__ w, float eps, const float* __restrict__ w2,
+                         float eps2, TX* x, int H) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int64_t base = (int64_t)blockIdx.x * H;
+  float keep[NA_VECS][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int p = 0; p < NA_VECS; ++p) {
+    const int c = (p * NA_THREADS + threadIdx.x) * 8;
+    if (c < H) {
+      on_load8(y + base + c, keep[p], true);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += keep[p][e] * keep[p][e];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  float ss2 = 0.0f;
+#pragma unroll
+  for (int p = 0; p < NA_VECS; ++p) {
+    const int c = (p * NA_THREADS + threadIdx.x) * 8;
+    if (c < H) {
+      float hv[8], wv[8];
+      on_load8(h + base + c, hv, true);
+      on_load8(w + c, wv, false);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        hv[e] += keep[p][e] * inv * wv[e];
+        keep[p][e] = hv[e];
+        ss2 += hv[e] * hv[e];
+      }
+      on_store8(h + base + c, hv);
+    }
+  }
+  ss2 = block_sum(ss2, red);
+  const float inv2 = 1.0f / sqrtf(ss2 / (float)H + eps2);
+#pragma unroll
+  for (int p = 0; p < NA_VECS; ++p) {
+    const int c = (p * NA_THREADS + threadIdx.x) * 8;
+    if (c < H) {
+      float wv[8];
+      on_load8(w2 + c, wv, false);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) keep[p][e] *= inv2 * wv[e];
+      on_store8(x + base + c, keep[p]);
+    }
+  }
+}
+
+// The two-output norm and sum with 16-byte accesses (rows as above, float32 weights).
+template <typename TA>
+__global__ void __launch_bounds__(NA_THREADS)
+normed_sum2_vec_kernel(const TA* a, const TA* b, const float* __restrict__ wa, const float* __restrict__ wb, float eps,
+                       float coef, float* out, int H) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int64_t base = (int64_t)blockIdx.x * H;
+  float ka[NA_VECS][8], kb[NA_VECS][8];
+  float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+  for (int p = 0; p < NA_VECS; ++p) {
+    const int c = (p * NA_THREADS + threadIdx.x) * 8;
+    if (c < H) {
+      on_load8(a + base + c, ka[p], true);
+      on_load8(b + base + c, kb[p], true);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { sa += ka[p][e] * ka[p][e]; sb += kb[p][e] * kb[p][e]; }
+    }
+  }
+  sa = block_sum(sa, red);
+  sb = block_sum(sb, red);
+  const float ia = coef / sqrtf(sa / (float)H + eps), ib = coef / sqrtf(sb / (float)H + eps);
+#pragma unroll
+  for (int p = 0; p < NA_VECS; ++p) {
+    const int c = (p * NA_THREADS + threadIdx.x) * 8;
+    if (c < H) {
+      float wx[8], wy[8], o[8];
+      on_load8(wa + c, wx, false);
+      on_load8(wb + c, wy, false);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = ka[p][e] * ia * wx[e] + kb[p][e] * ib * wy[e];
+      on_store8(out + base + c, o);
+    }
+  }
+}
+
 // Two sublayer outputs side by side, each normed over the row with its own weight, then averaged:
 //   out[t] = coef * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb), float32.
 __global__ void __launch_bounds__(NA_THREADS)
@@ -238,6 +382,33 @@ __global__ void gelu_vec_kernel(const TI* z, TO* out, int64_t n8, int kind) {
 
 using namespace exl3;
 
+extern "C" int exl3_norm_add_norm(float* h, const void* y, int y_dtype, const void* w, int w_dtype, float eps,
+                                  const void* w2, int w2_dtype, float eps2, void* x, int x_dtype, int T, int H,
+                                  cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || H < 1 || y == nullptr || w == nullptr || w2 == nullptr || x == nullptr) {
+    set_error("norm_add_norm: bad arguments T=%d H=%d", T, H);
+    return ERR_BAD_ARGUMENT;
+  }
+  const bool vec = H % 8 == 0 && H <= NA_THREADS * 8 * NA_VECS && w_dtype == DT_F32 && w2_dtype == DT_F32 &&
+                   aligned16(h) && aligned16(y) && aligned16(w) && aligned16(w2) && aligned16(x);
+  const float* wf = static_cast<const float*>(w);
+  const float* w2f = static_cast<const float*>(w2);
+  if (vec && y_dtype == DT_BF16 && x_dtype == DT_BF16)
+    launch_pdl(norm_add_norm_vec_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(NA_THREADS), 0, stream, h,
+               static_cast<const __nv_bfloat16*>(y), wf, eps, w2f, eps2, static_cast<__nv_bfloat16*>(x), H);
+  else if (vec && y_dtype == DT_F32 && x_dtype == DT_BF16)
+    launch_pdl(norm_add_norm_vec_kernel<float, __nv_bfloat16>, dim3(T), dim3(NA_THREADS), 0, stream, h,
+               static_cast<const float*>(y), wf, eps, w2f, eps2, static_cast<__nv_bfloat16*>(x), H);
+  else if (vec && y_dtype == DT_F32 && x_dtype == DT_F32)
+    launch_pdl(norm_add_norm_vec_kernel<float, float>, dim3(T), dim3(NA_THREADS), 0, stream, h,
+               static_cast<const float*>(y), wf, eps, w2f, eps2, static_cast<float*>(x), H);
+  else
+    launch_pdl(norm_add_norm_kernel, dim3(T), dim3(NA_THREADS), 0, stream, h, y, y_dtype, w, w_dtype, eps, w2, w2_dtype,
+               eps2, x, x_dtype, H);
+  return launch_status("norm_add_norm");
+}
+
 extern "C" int exl3_normed_sum2(const void* a, const void* b, int ab_dtype, const void* wa, const void* wb, int w_dtype,
                                 float eps, float coef, float* out, int T, int H, cudaStream_t stream) {
   if (T == 0) return 0;
@@ -245,7 +416,17 @@ extern "C" int exl3_normed_sum2(const void* a, const void* b, int ab_dtype, cons
     set_error("normed_sum2: bad arguments T=%d H=%d", T, H);
     return ERR_BAD_ARGUMENT;
   }
-  launch_pdl(normed_sum2_kernel, dim3(T), dim3(NA_THREADS), 0, stream, a, b, ab_dtype, wa, wb, w_dtype, eps, coef, out, H);
+  const bool vec = H % 8 == 0 && H <= NA_THREADS * 8 * NA_VECS && w_dtype == DT_F32 && aligned16(a) && aligned16(b) &&
+                   aligned16(wa) && aligned16(wb) && aligned16(out);
+  if (vec && ab_dtype == DT_BF16)
+    launch_pdl(normed_sum2_vec_kernel<__nv_bfloat16>, dim3(T), dim3(NA_THREADS), 0, stream,
+               static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), static_cast<const float*>(wa),
+               static_cast<const float*>(wb), eps, coef, out, H);
+  else if (vec && ab_dtype == DT_F32)
+    launch_pdl(normed_sum2_vec_kernel<float>, dim3(T), dim3(NA_THREADS), 0, stream, static_cast<const float*>(a),
+               static_cast<const float*>(b), static_cast<const float*>(wa), static_cast<const float*>(wb), eps, coef, out, H);
+  else
+    launch_pdl(normed_sum2_kernel, dim3(T), dim3(NA_THREADS), 0, stream, a, b, ab_dtype, wa, wb, w_dtype, eps, coef, out, H);
   return launch_status("normed_sum2");
 }
 

@@ -32,6 +32,7 @@ __device__ inline void qp_store(void* p, int dtype, int64_t i, float v) {
 }
 
 constexpr int QP_WARPS = 4;
+constexpr int QP_TABLE = 128;                    // pairs whose sine and cosine a block works out once for its token
 
 struct QkPrepArgs {
   const void* x; int x_dtype; int64_t ld; int q_off, k_off, v_off;
@@ -58,6 +59,19 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qk_prep_kernel(QkPrepArgs a) {
   const int in_page = a.k_pool != nullptr ? pos % a.page : 0;
   const int jobs = a.nh + a.nkv + (a.v_off >= 0 ? a.nkv : 0);
   const float fpos = (float)pos;
+  // the token's sines and cosines (times mscale), once for all its heads
+  __shared__ float s_sn[QP_TABLE], s_cs[QP_TABLE];
+  const int half = a.rot >> 1;
+  const bool table = half <= QP_TABLE;
+  if (table) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      float sn, cs;
+      rope_sincos(fpos, a.f_hi[i], a.f_lo ? a.f_lo[i] : 0.0f, &sn, &cs);
+      s_sn[i] = sn * a.mscale;
+      s_cs[i] = cs * a.mscale;
+    }
+    __syncthreads();
+  }
   for (int job = warp; job < jobs; job += QP_WARPS) {
     const bool is_q = job < a.nh;
     const bool is_k = !is_q && job < a.nh + a.nkv;
@@ -111,7 +125,6 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qk_prep_kernel(QkPrepArgs a) {
       out = a.k_out; out_dtype = a.k_out_dtype;
       dst = ((int64_t)t * a.nkv + head) * a.hd_pad;
     }
-    const int half = a.rot >> 1;
     for (int e = lane; e < a.hd_pad; e += 32) {
       float v = 0.0f;
       if (e < a.hd) {
@@ -123,9 +136,14 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qk_prep_kernel(QkPrepArgs a) {
           else { second = e >= half; i = second ? e - half : e; pe = second ? e - half : e + half; }
           const float o = sm[pe] * inv * (w ? qp_load(w, a.w_dtype, pe) : 1.0f);
           float sn, cs;
-          rope_sincos(fpos, a.f_hi[i], a.f_lo ? a.f_lo[i] : 0.0f, &sn, &cs);
-          sn *= a.mscale;
-          cs *= a.mscale;
+          if (table) {
+            sn = s_sn[i];
+            cs = s_cs[i];
+          } else {
+            rope_sincos(fpos, a.f_hi[i], a.f_lo ? a.f_lo[i] : 0.0f, &sn, &cs);
+            sn *= a.mscale;
+            cs *= a.mscale;
+          }
           v = second ? fmaf(v, cs, o * sn) : fmaf(v, cs, -o * sn);
         }
         v *= mul;

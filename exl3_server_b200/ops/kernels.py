@@ -764,6 +764,42 @@ def norm_add(h: torch.Tensor, y: Optional[torch.Tensor], weight: Optional[torch.
     return x
 
 
+def norm_add_norm(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, weight2: torch.Tensor,
+                  eps2: float, x_dtype: torch.dtype) -> torch.Tensor:
+    """``h += y * rsqrt(mean(y^2) + eps) * weight`` in place (float32) and, in the same kernel, the norm of the new
+    residual: returns ``h * rsqrt(mean(h^2) + eps2) * weight2`` in ``x_dtype``."""
+    T, H = h.shape
+    if h.dtype != torch.float32:
+        raise KernelLibraryError("norm_add_norm: the residual stream must be float32")
+    _contig(h, "h")
+    _contig(y, "y")
+    if tuple(y.shape) != (T, H) or weight.numel() != H or weight2.numel() != H:
+        raise KernelLibraryError(f"norm_add_norm: y {tuple(y.shape)} / weights do not fit h {tuple(h.shape)}")
+    x = torch.empty((T, H), dtype=x_dtype, device=h.device)
+    _check(library().exl3_norm_add_norm(
+        _ptr(h), _ptr(y), _c_int(dtype_code(y.dtype)), _ptr(weight), _c_int(dtype_code(weight.dtype)), _c_float(eps),
+        _ptr(weight2), _c_int(dtype_code(weight2.dtype)), _c_float(eps2), _ptr(x), _c_int(dtype_code(x.dtype)),
+        _c_int(T), _c_int(H), _stream()), "norm_add_norm")
+    return x
+
+
+def gemv_bf16_gelu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+                   tanh: bool = False) -> torch.Tensor:
+    """``gelu(x @ w.T (+ bias))`` for at most 16 rows of x, the activation (exact, or by the tanh formula) in the
+    projection's own epilogue."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelLibraryError(f"gemv_bf16_gelu: x {tuple(x.shape)} and w {tuple(w.shape)} must be bfloat16 and fit")
+    _contig(x, "x")
+    _contig(w, "w")
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _check(library().exl3_gemv_bf16_gelu(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(dtype_code(out.dtype)),
+                                         _c_int(M), _c_int(N), _c_int(K), _c_int(1 if tanh else 0), _stream()),
+           "gemv_bf16_gelu")
+    return out
+
+
 def xielu(z: torch.Tensor, pq: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """xIELU of every element with the raw parameter pair ``pq`` (see outnorm.cu)."""
     _contig(z, "z")
@@ -859,12 +895,14 @@ def attn_prefill_tc_status() -> int:
 def attn_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     block_table: torch.Tensor, row_start: torch.Tensor, row_pos0: torch.Tensor,
                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, heads: int, kv_heads: int,
-                    head_dim: int, page: int, window: int, scale: float, variant: int = 0) -> torch.Tensor:
+                    head_dim: int, page: int, window: int, scale: float, variant: int = 0, chunk: int = 0,
+                    sink: bool = False) -> torch.Tensor:
     """Causal attention of whole prompts on tcgen05 tensor cores (tiles of 128 queries; see
     attention_prefill_tc.cu).  ``k_pool`` / ``v_pool``: one layer's ``[pages, kv_heads, 64, head_dim]``.
     ``variant``: 0 lets the kernel choose by the number of blocks between a tile a block, four blocks per SM (heads
     of 64) and two tiles a block (the list's first with its last, and so on: list the tiles with the most keys
-    to visit first); 1, 2 and 3 force one of them (the same numbers every way)."""
+    to visit first); 1, 2 and 3 force one of them (the same numbers every way).  ``chunk`` and ``sink`` as in
+    ``attn_tokens_ex``."""
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelLibraryError("attn_prefill_tc: q, cache and out differ in element type")
     _contig(k_pool, "k_pool")
@@ -874,7 +912,8 @@ def attn_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
         _ptr(q), _c_int64(q_row_stride), _c_int(q.shape[0]), _ptr(out), _ptr(k_pool), _ptr(v_pool),
         _c_int64(pool_rows), _ptr(block_table), _c_int(block_table.stride(0)), _ptr(row_start), _ptr(row_pos0),
         _ptr(tile_seq), _ptr(tile_q0), _c_int(n_tiles), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
-        _c_int(page), _c_int(window), _c_float(scale), _c_int(variant), _stream()), "attn_prefill_tc")
+        _c_int(page), _c_int(window), _c_int(chunk), _c_int(1 if sink else 0), _c_float(scale), _c_int(variant),
+        _stream()), "attn_prefill_tc")
     return out
 
 
@@ -910,7 +949,7 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
                 kv_heads: int, head_dim: int, page: int, window: int, scale: float, split_keys: int,
                 max_splits: int, scratch: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor] = None,
                 rot: int = 0, pos_scale: float = 1.0, write_new: bool = False, head_split: int = 1,
-                in_block: int = 0, twins: int = 1) -> torch.Tensor:
+                in_block: int = 0, twins: int = 1, chunk: int = 0, sink: bool = False) -> torch.Tensor:
     """Attention of T query tokens over the paged cache on the tensor cores (see attention_decode.cu);
     arguments and scratch as ``attn_tokens``.  With ``write_new``, ``q`` is the fused q|k|v output of the
     projection, every token is its sequence's only new one and the cache holds the positions before it: the
@@ -923,7 +962,8 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
     chunks; the first block merges and reads the second one's records out of its shared memory): no scratch, no
     tickets; results differ from the other way's by rounding (another order of the same sums).  ``twins`` 2 (with
     ``in_block`` 1 or 2, an even ``head_split`` and groups of up to 8 heads): a block takes two groups of query heads
-    of a kv head, whose warps walk the same pages out of the same rings; changes no result."""
+    of a kv head, whose warps walk the same pages out of the same rings; changes no result.  ``chunk`` and ``sink`` as
+    in ``attn_tokens_ex``."""
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelLibraryError("attn_decode: q, cache and out differ in element type")
     _contig(k_pool, "k_pool")
@@ -938,8 +978,8 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
     _check(library().exl3_attn_decode(
         _ptr(q), _c_int64(q_row_stride), _ptr(out), _ptr(k_pool), _ptr(v_pool), _c_int64(pool_rows),
         _ptr(block_table), _c_int(block_table.stride(0)), _ptr(tok_pos), _ptr(tok_seq), _c_int(T), _c_int(heads),
-        _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale), _c_int(split_keys),
-        _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), hi, lo, _c_int(rot),
+        _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_int(chunk), _c_int(1 if sink else 0),
+        _c_float(scale), _c_int(split_keys), _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), hi, lo, _c_int(rot),
         _c_float(pos_scale), _c_int(1 if write_new else 0), _c_int(head_split), _c_int(int(in_block)),
         _c_int(int(twins)), _stream()), "attn_decode")
     return out

@@ -119,6 +119,18 @@ class RawNormed:
         return (x_raw.float() * (inv * out_scale)[:, None]).to(x_raw.dtype)
 
 
+class ReadyNormed:
+    """A norm's output over the residual as it stands, already computed by the kernel that last changed the residual
+    (``x`` in the activation type)."""
+
+    def __init__(self, x: torch.Tensor):
+        self.x = x
+
+    def materialize(self, out_scale: float = 1.0, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = self.x if rows is None else self.x.index_select(0, rows.long())
+        return x if out_scale == 1.0 else (x.float() * out_scale).to(x.dtype)
+
+
 class NormAfter:
     """An offer to a part's last projection: instead of returning its output ``y`` to be added later, it may,
     where its kernel can, add ``y * scale`` to the residual ``stream.h`` itself and leave what ``norm`` needs

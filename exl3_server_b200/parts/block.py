@@ -96,12 +96,26 @@ class SandwichBlock:
             if n is not None and float(n.spec.params.get("scale", 1.0)) != float(spec.residual_scale):
                 raise ValueError("sandwich: the output norms' scale must be the layer's residual scale")
 
-    def forward(self, stream: ResidualStream, batch, kv, state) -> None:
+    takes_after = True
+
+    def forward(self, stream: ResidualStream, batch, kv, state, after=None) -> None:
+        """``after``: the norm that the next block applies first, if the caller knows it: the kernel that adds this
+        block's last sublayer to the residual then also computes that norm (as it does for this block's second
+        sublayer)."""
         x = self.mixer_norm.add_norm(stream)
-        self.mixer_out_norm.add_normed(stream, self.mixer.forward(x, batch, kv, state), want_x=False)
+        y = self.mixer.forward(x, batch, kv, state)
+        nxt = self.feed_forward_norm if self.feed_forward is not None else after
+        self._add(self.mixer_out_norm, stream, y, nxt)
         if self.feed_forward is not None:
             x = self.feed_forward_norm.add_norm(stream)
-            self.feed_forward_out_norm.add_normed(stream, self.feed_forward.forward(x, batch), want_x=False)
+            self._add(self.feed_forward_out_norm, stream, self.feed_forward.forward(x, batch), after)
+
+    @staticmethod
+    def _add(out_norm, stream: ResidualStream, y, then_norm) -> None:
+        if then_norm is not None and hasattr(out_norm, "add_normed_then") and hasattr(then_norm, "weight"):
+            out_norm.add_normed_then(stream, y, then_norm)
+        else:
+            out_norm.add_normed(stream, y, want_x=False)
 
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in (self.mixer, self.feed_forward, self.mixer_norm, self.feed_forward_norm,

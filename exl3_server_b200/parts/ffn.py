@@ -98,8 +98,12 @@ def _gelu_tanh(z: torch.Tensor, tensors, out_dtype):
     return K.activation(z, out_dtype, "gelu_tanh")
 
 
-def _no_fused(linear: Linear, x: torch.Tensor, tensors, out_dtype):
-    return None
+def _gelu_fused(linear: Linear, x: torch.Tensor, tensors, out_dtype):
+    return linear.gelu(x, out_dtype, tanh=False)
+
+
+def _gelu_tanh_fused(linear: Linear, x: torch.Tensor, tensors, out_dtype):
+    return linear.gelu(x, out_dtype, tanh=True)
 
 
 def _no_prepare(tensors) -> None:
@@ -110,8 +114,8 @@ def _no_prepare(tensors) -> None:
 #          function(linear, x, {suffix: tensor}, out_dtype) -> activated projection or None,
 #          function({suffix: tensor}) called once when the part is built)
 ACTIVATIONS = {"xielu": ((("act", (2,)),), _xielu, _xielu_fused, _xielu_prepare),
-               "gelu": ((), _gelu, _no_fused, _no_prepare),               # z/2 (1 + erf(z / sqrt 2))
-               "gelu_tanh": ((), _gelu_tanh, _no_fused, _no_prepare)}     # z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+               "gelu": ((), _gelu, _gelu_fused, _no_prepare),             # z/2 (1 + erf(z / sqrt 2))
+               "gelu_tanh": ((), _gelu_tanh, _gelu_tanh_fused, _no_prepare)}   # z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 
 
 class DenseFeedForward:

@@ -20,7 +20,7 @@ import torch
 
 from ..ops import kernels as K
 from ..weights.loader import TensorSpec
-from .base import BuildContext, ResidualStream
+from .base import BuildContext, ReadyNormed, ResidualStream
 from .registry import register_norm
 from .spec import NormSpec
 
@@ -50,7 +50,7 @@ class RMSNorm:
         projection before this norm) as well as a tensor."""
         left = stream.take_normed(self)
         if left is not None:
-            if rows is None and raw_ok and out_scale == 1.0:
+            if rows is None and raw_ok and out_scale == 1.0 and not isinstance(left, ReadyNormed):
                 return left
             return left.materialize(out_scale, rows)
         y, s = stream.take()
@@ -75,6 +75,16 @@ class RMSNorm:
         x = K.norm_add(stream.h, y, self.weight if y is not None else None, self.spec.eps, x_dtype)
         stream.act = x if x is not None else stream.h
         return stream.act
+
+    def add_normed_then(self, stream: ResidualStream, y: torch.Tensor, then_norm) -> None:
+        """``add_normed`` and, in the same kernel, the output of ``then_norm`` (the next sublayer's input norm) over
+        the new residual, left in the stream for ``then_norm.add_norm`` to pick up."""
+        if stream.pending is not None:
+            raise RuntimeError("the residual stream holds an output that was not folded in")
+        x = K.norm_add_norm(stream.h, y, self.weight, self.spec.eps, then_norm.weight, then_norm.spec.eps,
+                            then_norm.out_dtype)
+        stream.act = None
+        stream.normed = (then_norm, ReadyNormed(x))
 
     def fuse_args(self):
         """``(weight, eps, width)`` for a projection kernel that prepares this norm (see ``NormAfter``)."""

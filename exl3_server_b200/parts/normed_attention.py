@@ -16,9 +16,12 @@ Per token ``q, k, v = r Wq^T, r Wk^T, r Wv^T`` (one joint matrix; biases optiona
 * ``softmax_scale`` of the spec multiplies the scores.
 
 ``y = concat_h(o_h) Wo^T`` (+ bias).  Norms, rotation, mixing, scores and softmax are float32.  One kernel
-(``kernels.qk_prep``) does everything between the projection and the attention and writes the cache; the attention
-is the CUDA-core kernel in its general form (``kernels.attn_tokens_ex``), the same for prompts, portions of prompts
-and single tokens.  Head sizes are padded to a multiple of 8 in the cache (zeros), so any even size runs.
+(``kernels.qk_prep``) does everything between the projection and the attention and writes the cache.  In bfloat16
+with keys and values of 64 or 128 features the attention is the tensor-core kernels' (tcgen05 for prompts, the TMA
+page stream for steps of few tokens), which take the sink and the blocks as parameters; everything else (float32,
+other sizes, values of another width than keys) is the CUDA-core kernel in its general form
+(``kernels.attn_tokens_ex``), the same for prompts, portions of prompts and single tokens.  Head sizes are padded to
+a multiple of 8 in the cache (zeros), so any even size runs.
 
 Tensor names under the mixer's prefix: ``q``, ``k``, ``v``, ``o`` (biases: the name + ``.b``), ``q.norm``,
 ``k.norm``, ``vmix``.
@@ -34,7 +37,7 @@ import torch
 
 from ..ops import kernels as K
 from ..weights.loader import TensorSpec
-from .attention import BUSY_ITEMS, SPLIT_KEYS
+from .attention import BUSY_ITEMS, SPLIT_KEYS, Attention
 from .base import BuildContext, KVRequest, StateRequest
 from .linear import Linear
 from .registry import position_class, register_mixer
@@ -97,6 +100,11 @@ class NormedAttention:
         pos = spec.position or PositionSpec(kind="none", dims=0)
         self.position = position_class(pos.kind)(pos, d, ctx)
         self.rot = int(self.position.spec.dims)
+        # How the tensor-core kernels cut a step's work is the attention part's business: a block of ``chunk``
+        # positions bounds a query's keys as a window of that many keys does.
+        self._cuts = Attention.__new__(Attention)
+        self._cuts.spec = MixerSpec(kind="attention", width=spec.width, heads=H, kv_heads=G, head_dim=self.d_pad,
+                                    window=self.chunk)
 
     # -- what a part that projects for several mixers at once needs -----------------------------------------------
     def input_weight(self) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
@@ -134,6 +142,8 @@ class NormedAttention:
                          self.position.mscale, 1.0, mix, batch.tok_pos, batch.tok_seq, kv.block_table, kv.page_size,
                          self.ctx.dtype, kv.k, kv.v)
         out = torch.empty((T, H * self.dv_pad), dtype=self.ctx.dtype, device=proj.device)
+        if self._tensor_cores(q, out, batch, kv):
+            return self.o(out, out_dtype=self.o.wide_dtype(T))
         split = max(SPLIT_KEYS, kv.page_size)
         if split % kv.page_size:
             split = kv.page_size * (split // kv.page_size + 1)
@@ -149,6 +159,36 @@ class NormedAttention:
         K.attn_tokens_ex(q, q.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T, H, G,
                          self.d_pad, self.dv_pad, kv.page_size, 0, self.chunk, self.sink, self.scale, split, n, scratch)
         return self.o(out, out_dtype=self.o.wide_dtype(T))
+
+    def _tensor_cores(self, q: torch.Tensor, out: torch.Tensor, batch, kv) -> bool:
+        """bfloat16 with keys and values of 64 or 128 features: prompts through the tcgen05 kernel, steps of few
+        tokens through the kernel that streams pages by TMA, both with the sink and the blocks of positions as
+        parameters.  False when the sizes are not theirs (the CUDA-core kernel then takes the step)."""
+        if self.ctx.dtype != torch.bfloat16 or self.d_pad != self.dv_pad or self.d_pad != self.d:
+            return False
+        H, G, d, T = self.H, self.G, self.d, q.shape[0]
+        if batch.max_new > 1 and batch.tiles and K.attn_prefill_tc_supported(torch.bfloat16, d, kv.page_size):
+            tile_seq, tile_q0, n_tiles = batch.tiles[128]
+            key = ("attn_prefill_variant", H, d, self.chunk)
+            variant = batch.memo.get(key)
+            if variant is None:
+                variant = batch.memo[key] = self._cuts._prefill_variant(batch.tile_keys.get(128), kv.page_size, q.device)
+            K.attn_prefill_tc(q, q.stride(0), out, kv.k, kv.v, kv.block_table, batch.row_start, batch.row_pos0, tile_seq,
+                              tile_q0, n_tiles, H, G, d, kv.page_size, 0, self.scale, variant=variant, chunk=self.chunk,
+                              sink=self.sink)
+            return True
+        if not K.attn_decode_supported(torch.bfloat16, T, H, G, d, kv.page_size, kv.page_size, 1):
+            return False
+        split, head_split, in_block = self._cuts._decode_split(T, batch.max_kv_len, kv.page_size, q.device)
+        head_split, twins = self._cuts._decode_twins(head_split, in_block)
+        n = self._cuts._chunks(batch.max_kv_len, split)
+        scratch = None
+        if n > 1 and not in_block:
+            scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, H, d, n) // 4)
+        K.attn_decode(q, q.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T, H, G, d,
+                      kv.page_size, 0, self.scale, split, n, scratch, head_split=head_split, in_block=in_block,
+                      twins=twins, chunk=self.chunk, sink=self.sink)
+        return True
 
     def _chunks(self, max_kv_len: int, split: int) -> int:
         """The most pieces of ``split`` keys that a token's visible keys can touch."""

@@ -57,11 +57,23 @@ CONFIGS = {
         NikodraLayer("wkv", {"heads": 2, "dim": 64, "decay_rank": 16}, dense(192)),
         NikodraLayer("attention", attn(8, 2, 64, 128, 0.125, v_mix=True), None),
     ]),
+    # keys and values of 64 and of 128 features: the sizes of the tensor-core attention kernels, with the sink, blocks of
+    # 100 positions (edges inside pages), eight query heads on a kv head, part of a head rotated, mixed values
+    "tensor": NikodraConfig(vocab=200, width=128, norm_eps=1e-6, residual_mult=0.5, bigram=BIGRAM, layers=[
+        NikodraLayer("attention", attn(4, 2, 64, 64, 0.125, dims=32, scaling=(4.0, 256, 32.0, 1.0), v_mix=True), dense(128)),
+        NikodraLayer("parallel", par(attn(4, 2, 128, 128, 0.09), 100, 2, 32, 32, (0.9, 0.99)), None),
+        NikodraLayer("attention", attn(8, 1, 128, 128, 0.09, base=1000000.0), None),
+        NikodraLayer("attention", attn(6, 2, 64, 64, 0.125, v_mix=True), dense(96)),
+    ]),
     # one mechanism alone
     "only_attention": NikodraConfig(vocab=128, width=80, norm_eps=1e-6, residual_mult=0.5, bigram=None, layers=[
         NikodraLayer("attention", attn(4, 2, 32, 24, 0.18, scaling=(4.0, 128, 32.0, 1.0)), None)]),
     "only_parallel": NikodraConfig(vocab=128, width=80, norm_eps=1e-6, residual_mult=0.5, bigram=None, layers=[
         NikodraLayer("parallel", par(attn(4, 4, 16, 16, 0.25), 70, 4, 16, 32, (0.5, 0.9, 0.99, 0.999)), None)]),
+    "only_attention_64": NikodraConfig(vocab=128, width=80, norm_eps=1e-6, residual_mult=0.5, bigram=None, layers=[
+        NikodraLayer("attention", attn(4, 2, 64, 64, 0.09, dims=32, scaling=(4.0, 128, 32.0, 1.0)), None)]),
+    "only_parallel_64": NikodraConfig(vocab=128, width=80, norm_eps=1e-6, residual_mult=0.5, bigram=None, layers=[
+        NikodraLayer("parallel", par(attn(4, 2, 64, 64, 0.09), 70, 2, 16, 16, (0.9, 0.99)), None)]),
     "only_wkv": NikodraConfig(vocab=128, width=80, norm_eps=1e-6, residual_mult=0.5, bigram=None, layers=[
         NikodraLayer("wkv", {"heads": 4, "dim": 24}, None)]),
     "only_embedding": NikodraConfig(vocab=128, width=80, norm_eps=1e-6, residual_mult=0.5, bigram=BIGRAM, layers=[

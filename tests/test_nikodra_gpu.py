@@ -19,8 +19,9 @@ from plain_nikodra import PlainNikodra
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"mixed": [1, 2, 9, 64, 65, 150], "odd": [1, 3, 20, 64, 66, 131], "wide": [3, 17, 63, 128, 129, 300],
+LENGTHS = {"mixed": [1, 2, 9, 64, 65, 150], "tensor": [1, 2, 40, 128, 129, 330], "odd": [1, 3, 20, 64, 66, 131], "wide": [3, 17, 63, 128, 129, 300],
            "only_attention": [1, 2, 31, 64, 129, 140], "only_parallel": [1, 2, 31, 64, 129, 141],
+           "only_attention_64": [1, 2, 31, 64, 129, 140], "only_parallel_64": [1, 2, 31, 64, 129, 141],
            "only_wkv": [1, 2, 31, 64, 129, 140], "only_embedding": [1, 2, 31, 64, 129, 140]}
 
 
@@ -91,7 +92,7 @@ def test_float32_cuttings_agree_closely(folders, name):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["mixed", "odd"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "tensor"])
 def test_portions_of_a_prompt(folders, name, dtype):
     """A prompt fed in portions of many sizes, down to two tokens, some ending on a page border, on a block's edge
     (50 and 7 positions) and inside one, and one long enough for the recurrences' chunks to run side by side."""
@@ -155,9 +156,10 @@ def _marked_model(src, folder, name):
     tensors["embed"][:, 1] = 0.5
     tensors["embed"][marked, 0] = 2.0
     tensors["l0.norm1"][:2] = 0.0
-    qn, kn = ("l0.mix.left.q", "l0.mix.left.k") if name == "only_parallel" else ("l0.mix.q", "l0.mix.k")
+    par = CONFIGS[name].layers[0].type == "parallel"
+    qn, kn = ("l0.mix.left.q", "l0.mix.left.k") if par else ("l0.mix.q", "l0.mix.k")
     m = CONFIGS[name].layers[0].mixer
-    d = (m["left"] if name == "only_parallel" else m)["dim"]
+    d = (m["left"] if par else m)["dim"]
     for w, col in ((tensors[qn], 1), (tensors[kn], 0)):
         w[:, col] = 0.0
         w.view(-1, d, w.shape[1])[:, d // 2:, col] = 3.0
@@ -168,7 +170,9 @@ def _marked_model(src, folder, name):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name, places", [("only_attention", [0, 1, 63, 64, 127, 128, 300]),
-                                           ("only_parallel", [630, 629, 639, 640, 690, 699])])
+                                           ("only_parallel", [630, 629, 639, 640, 690, 699]),
+                                           ("only_attention_64", [0, 1, 63, 64, 127, 128, 300]),
+                                           ("only_parallel_64", [630, 629, 639, 640, 690, 699])])
 def test_a_key_that_stands_out(folders, tmp_path, name, places, dtype):
     """The marked key sits first, second, on both sides of page borders and hundreds of tokens back (plain attention),
     and just outside, first in, on a page border inside and last in the block of 70 positions that the last queries
@@ -184,7 +188,7 @@ def test_a_key_that_stands_out(folders, tmp_path, name, places, dtype):
         toks = list(base)
         toks[place] = marked
         want = pm.logits(toks).numpy()
-        visible = name == "only_attention" or place >= 630
+        visible = CONFIGS[name].layers[0].type == "attention" or place >= 630
         gap = rel_err(pm.logits(base).numpy()[-20:], want[-20:])
         if visible:
             assert gap > 0.3, (place, gap)                # the test can see the key
@@ -195,7 +199,7 @@ def test_a_key_that_stands_out(folders, tmp_path, name, places, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["mixed", "odd"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "tensor"])
 def test_long_decoding(folders, name, dtype):
     """Three tokens of prompt, then 200 decoded one by one over three page borders and several blocks' edges, two
     sequences side by side."""
@@ -241,7 +245,7 @@ def test_a_reused_slot_shows_nothing_of_its_former_owner(folders, dtype):
     eng.cache.check()
 
 
-@pytest.mark.parametrize("name", ["mixed", "odd", "wide"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "wide", "tensor"])
 def test_greedy_generation_through_the_entry_point(folders, name):
     from exl3_server_b200 import GenerateOptions
     folder = folders[name]
@@ -269,8 +273,8 @@ def test_residual_stream_layer_by_layer(folders):
     eng = engine_for(folder, "float32")
     seen = []
     for b in eng.model.blocks:
-        def wrapped(stream, batch, kv, state, f=b.forward):
-            f(stream, batch, kv, state)
+        def wrapped(stream, *args, f=b.forward, **kwargs):
+            f(stream, *args, **kwargs)
             seen.append(stream.h.clone())
         b.forward = wrapped
     s = eng.open()

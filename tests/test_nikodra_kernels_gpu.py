@@ -304,3 +304,84 @@ def test_head_norm_gate_normed_sum_and_activations(dt):
         close(k_.activation(z.to(DEV), dt, "gelu_tanh"),
               0.5 * zd * (1 + torch.tanh(math.sqrt(2 / math.pi) * (zd + 0.044715 * zd ** 3))), dt)
         close(k_.activation(z.to(DEV), torch.float32, "tanh"), torch.tanh(zd), torch.float32)
+
+
+@pytest.mark.parametrize("y_dt", TYPES)
+@pytest.mark.parametrize("H", [96, 2304])
+def test_norm_add_norm(y_dt, H):
+    """The norm on a sublayer's output, the residual sum and the next input norm in one kernel; rows longer than a
+    thread keeps in registers too."""
+    g = torch.Generator().manual_seed(8)
+    T = 5
+    h = torch.randn(T, H, generator=g)
+    y = (torch.randn(T, H, generator=g) * 4).to(y_dt)
+    w, w2 = 0.5 + 0.1 * torch.randn(H, generator=g), 1 + 0.1 * torch.randn(H, generator=g)
+    hd = h.clone().to(DEV)
+    for x_dt in TYPES:
+        hd = h.clone().to(DEV)
+        x = K().norm_add_norm(hd, y.to(DEV), w.to(DEV), 1e-5, w2.to(DEV), 2e-6, x_dt)
+        yd = y.double()
+        want_h = h.double() + yd / torch.sqrt((yd * yd).mean(-1, keepdim=True) + 1e-5) * w.double()
+        close(hd, want_h, torch.float32, "residual")
+        close(x, want_h / torch.sqrt((want_h * want_h).mean(-1, keepdim=True) + 2e-6) * w2.double(), x_dt, "next norm")
+
+
+def test_gelu_in_the_projection():
+    g = torch.Generator().manual_seed(9)
+    M, N, Kd = 5, 72, 128
+    x = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, Kd, generator=g) * 0.2).to(torch.bfloat16)
+    z = x.double() @ w.double().T
+    for tanh in (False, True):
+        got = K().gemv_bf16_gelu(x.to(DEV), w.to(DEV), None, torch.float32, tanh=tanh)
+        want = 0.5 * z * (1 + (torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)) if tanh else torch.erf(z / math.sqrt(2))))
+        close(got, want, torch.float32)
+
+
+@pytest.mark.parametrize("H, G, d, chunk, sink", [(4, 2, 64, 0, True), (8, 1, 128, 100, True), (6, 2, 64, 200, False),
+                                                   (4, 4, 128, 0, True)])
+def test_tensor_core_attention_for_single_tokens_with_sink_and_blocks(H, G, d, chunk, sink):
+    """The decode kernel's three ways of ending a row (one chunk; chunks merged through scratch; chunks merged inside
+    a block or a cluster) all count the sink, and its key range starts at the block's edge."""
+    g = torch.Generator().manual_seed(10)
+    k_ = K()
+    page, n_pages, width = 64, 40, 12
+    lens = [700, 1, 130, 65]
+    perm = torch.randperm(n_pages, generator=g)
+    bt = torch.full((len(lens), width), -1, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(lens):
+        need = (n + page - 1) // page
+        bt[b, :need] = perm[at:at + need].int()
+        at += need
+    kp = torch.randn(n_pages, G, page, d, generator=g).to(torch.bfloat16)
+    vp = torch.randn(n_pages, G, page, d, generator=g).to(torch.bfloat16)
+    queries = [(0, 699), (1, 0), (2, 129), (3, 64)]
+    T = len(queries)
+    q = torch.randn(T, H * d, generator=g).to(torch.bfloat16)
+    tok_seq = torch.tensor([b for b, _ in queries], dtype=torch.int32)
+    tok_pos = torch.tensor([p for _, p in queries], dtype=torch.int32)
+    scale = 0.9 / math.sqrt(d)
+    want = torch.zeros(T, H, d, dtype=torch.float64)
+    for t, (b, p) in enumerate(queries):
+        lo = p // chunk * chunk if chunk else 0
+        js = torch.arange(lo, p + 1)
+        pg = bt[b, js // page].long()
+        kk, vv = kp[pg, :, js % page].double(), vp[pg, :, js % page].double()
+        for h in range(H):
+            s = kk[:, h // (H // G)] @ q[t, h * d:(h + 1) * d].double() * scale
+            m = max(float(s.max()), 0.0) if sink else float(s.max())
+            e = torch.exp(s - m)
+            want[t, h] = (e / (e.sum() + (math.exp(-m) if sink else 0.0))) @ vv[:, h // (H // G)]
+    for split, in_block in ((1024, 0), (256, 0), (256, 1), (128, 2)):
+        n = (700 + split - 1) // split
+        if chunk:
+            n = min(n, (chunk + split - 2) // split + 1)
+        if in_block and not 1 < n <= 4 * in_block:
+            continue
+        scratch = torch.zeros(k_.attn_tokens_scratch_bytes(T, H, d, n) // 4 + 1, device=DEV) if n > 1 and not in_block else None
+        out = torch.empty(T, H * d, dtype=torch.bfloat16, device=DEV)
+        k_.attn_decode(q.to(DEV), H * d, out, kp.to(DEV), vp.to(DEV), bt.to(DEV), tok_pos.to(DEV), tok_seq.to(DEV), T, H, G, d,
+                       page, 0, scale, split, n, scratch, in_block=in_block, chunk=chunk, sink=sink)
+        close(out.reshape(T, H, d), want, torch.bfloat16, f"split {split} in_block {in_block}")
+    assert k_.attn_decode_status() == 0
