@@ -1,4 +1,4 @@
-"""A small single-GPU generation library for the Llama-family and Rigitar decoders, written for B200 (sm_100a).
+"""A small single-GPU generation library for the Llama-family, Rigitar and Nikodra decoders, written for B200 (sm_100a).
 
 Entry points::
 

@@ -260,18 +260,26 @@ __global__ void linear_scan_kernel(ScanArgs a, int phase) {
   }
 }
 
-// The same with a thread's column of S in registers, for key sizes of 16, 32, 64 and 128 and up to 256 values a
-// head: no shared-memory traffic for the state, and r, k and the decays read four at a time.  (With the state in
-// shared memory a token costs a warp five shared-memory instructions per key channel, which is what bounded the
+// The same with the state in registers, for key sizes of 16, 32, 64 and 128 and up to 128 values a head.  A column of
+// S is cut over LS_Q threads (a quarter of the key channels each), so a token costs a thread DK / 4 steps of its chain
+// instead of DK and a block has four times the warps to hide its loads behind; the four partial sums of an output
+// meet in shared memory once per stage of eight tokens.  r, k and the decays are read four at a time.  (With the whole
+// state in shared memory a token cost a warp five shared-memory instructions per key channel, which bounded the
 // kernel: 8,192 tokens of 32 heads of 64 x 64 took 0.94 ms a launch.)
+constexpr int LS_Q = 4;
+constexpr int LS_MAX_DV = 128;
+
 template <int MODE, int DK>
-__global__ void __launch_bounds__(256) linear_scan_reg_kernel(ScanArgs a, int phase) {
+__global__ void __launch_bounds__(LS_Q * LS_MAX_DV) linear_scan_reg_kernel(ScanArgs a, int phase) {
+  constexpr int DKQ = DK / LS_Q;
   __shared__ __align__(16) float sr[LS_STAGE * DK];
   __shared__ __align__(16) float sk[LS_STAGE * DK];
   __shared__ __align__(16) float sw[MODE == 0 ? LS_STAGE * DK : 4];
   __shared__ float sb[LS_STAGE];
   __shared__ float sA[DK];
+  extern __shared__ float ls_acc[];                  // [LS_STAGE][LS_Q][dvr] partial outputs
   const int dv = a.dv;
+  const int dvr = blockDim.x / LS_Q;                 // dv rounded up to whole warps
   pdl_wait();
   pdl_trigger();
   const int hd = blockIdx.x, c = blockIdx.y, b = blockIdx.z;
@@ -286,36 +294,38 @@ __global__ void __launch_bounds__(256) linear_scan_reg_kernel(ScanArgs a, int ph
     hi = min(lo + LS_CHUNK, t1);
     if (lo >= t1) return;
   }
-  const int j = threadIdx.x;
+  const int q = threadIdx.x / dvr, j = threadIdx.x - q * dvr;
   const bool col = j < dv;
+  const int i0 = q * DKQ;                            // this thread's key channels: i0 .. i0 + DKQ - 1
   float* st = a.state + ((int64_t)__ldcg(a.slot_ids + b) * a.heads + hd) * DK * dv;
   const int64_t rec = (int64_t)DK + (int64_t)DK * dv;
   float* snap = a.snap + ((int64_t)b * a.heads + hd) * DK * dv;
-  float S[DK];
+  float S[DKQ];
   if (phase == 1) {
 #pragma unroll
-    for (int i = 0; i < DK; ++i) S[i] = 0.0f;
-    for (int i = j; i < DK; i += blockDim.x) sA[i] = 1.0f;
+    for (int i = 0; i < DKQ; ++i) S[i] = 0.0f;
+    for (int i = threadIdx.x; i < DK; i += blockDim.x) sA[i] = 1.0f;
     if (c == 0 && col) {
 #pragma unroll
-      for (int i = 0; i < DK; ++i) snap[i * dv + j] = __ldcg(st + i * dv + j);
+      for (int i = 0; i < DKQ; ++i) snap[(i0 + i) * dv + j] = __ldcg(st + (i0 + i) * dv + j);
     }
   } else {
     const float* from = (phase == 2 && t1 - t0 > LS_CHUNK) ? snap : st;
 #pragma unroll
-    for (int i = 0; i < DK; ++i) S[i] = col ? __ldcg(from + i * dv + j) : 0.0f;
+    for (int i = 0; i < DKQ; ++i) S[i] = col ? __ldcg(from + (i0 + i) * dv + j) : 0.0f;
     if (phase == 2 && col) {
-      for (int p = 0; p < c; ++p) {
+#pragma unroll 2
+      for (int p = 0; p < c; ++p) {                  // the chunks before this one, in order
         const float* ab = a.ab + ((int64_t)ls_place(t0, b, p) * a.heads + hd) * rec;
 #pragma unroll
-        for (int i = 0; i < DK; ++i) S[i] = fmaf(__ldcg(ab + i), S[i], __ldcg(ab + DK + i * dv + j));
+        for (int i = 0; i < DKQ; ++i) S[i] = fmaf(__ldcg(ab + i0 + i), S[i], __ldcg(ab + DK + (i0 + i) * dv + j));
       }
     }
   }
   const float gamma = MODE == 1 ? a.decay[hd] : 0.0f;
   for (int s0 = lo; s0 < hi; s0 += LS_STAGE) {
     const int n = min(LS_STAGE, hi - s0);
-    __syncthreads();
+    __syncthreads();                                 // the stage before has been used, its outputs written
     for (int idx = threadIdx.x; idx < n * DK; idx += blockDim.x) {
       const int tt = idx / DK, i = idx - tt * DK;
       const int64_t t = s0 + tt;
@@ -327,6 +337,11 @@ __global__ void __launch_bounds__(256) linear_scan_reg_kernel(ScanArgs a, int ph
         sw[idx] = expf(-expf(z));
       }
     }
+    // the values of the stage's tokens, asked for before the barrier
+    float vj[LS_STAGE];
+#pragma unroll
+    for (int tt = 0; tt < LS_STAGE; ++tt)
+      vj[tt] = (col && tt < n) ? ls_load_act(a.v, a.v_dtype, (int64_t)(s0 + tt) * a.v_ld + (int64_t)hd * dv + j) : 0.0f;
     __syncthreads();
     if (MODE == 0) {
       const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -351,41 +366,44 @@ __global__ void __launch_bounds__(256) linear_scan_reg_kernel(ScanArgs a, int ph
         sA[i] = p;
       }
     }
-    if (col) {
-      // the values of the stage's tokens, asked for together
-      float vj[LS_STAGE];
 #pragma unroll
-      for (int tt = 0; tt < LS_STAGE; ++tt)
-        vj[tt] = tt < n ? ls_load_act(a.v, a.v_dtype, (int64_t)(s0 + tt) * a.v_ld + (int64_t)hd * dv + j) : 0.0f;
+    for (int tt = 0; tt < LS_STAGE; ++tt) {
+      if (tt < n) {
+        const float4* rr = reinterpret_cast<const float4*>(sr + tt * DK + i0);
+        const float4* kk = reinterpret_cast<const float4*>(sk + tt * DK + i0);
+        float acc0 = 0.0f, acc1 = 0.0f;
+        if (MODE == 0) {
+          const float4* ww = reinterpret_cast<const float4*>(sw + tt * DK + i0);
 #pragma unroll
-      for (int tt = 0; tt < LS_STAGE; ++tt) {
-        if (tt < n) {
-          const float4* rr = reinterpret_cast<const float4*>(sr + tt * DK);
-          const float4* kk = reinterpret_cast<const float4*>(sk + tt * DK);
-          float acc = 0.0f;
-          if (MODE == 0) {
-            const float4* ww = reinterpret_cast<const float4*>(sw + tt * DK);
-#pragma unroll
-            for (int i4 = 0; i4 < DK / 4; ++i4) {
-              const float4 r4 = rr[i4], k4 = kk[i4], w4 = ww[i4];
-              acc = fmaf(r4.x, S[4 * i4 + 0], acc); S[4 * i4 + 0] = fmaf(w4.x, S[4 * i4 + 0], k4.x * vj[tt]);
-              acc = fmaf(r4.y, S[4 * i4 + 1], acc); S[4 * i4 + 1] = fmaf(w4.y, S[4 * i4 + 1], k4.y * vj[tt]);
-              acc = fmaf(r4.z, S[4 * i4 + 2], acc); S[4 * i4 + 2] = fmaf(w4.z, S[4 * i4 + 2], k4.z * vj[tt]);
-              acc = fmaf(r4.w, S[4 * i4 + 3], acc); S[4 * i4 + 3] = fmaf(w4.w, S[4 * i4 + 3], k4.w * vj[tt]);
-            }
-            acc = fmaf(sb[tt], vj[tt], acc);
-          } else {
-#pragma unroll
-            for (int i4 = 0; i4 < DK / 4; ++i4) {
-              const float4 r4 = rr[i4], k4 = kk[i4];
-              S[4 * i4 + 0] = fmaf(gamma, S[4 * i4 + 0], k4.x * vj[tt]); acc = fmaf(r4.x, S[4 * i4 + 0], acc);
-              S[4 * i4 + 1] = fmaf(gamma, S[4 * i4 + 1], k4.y * vj[tt]); acc = fmaf(r4.y, S[4 * i4 + 1], acc);
-              S[4 * i4 + 2] = fmaf(gamma, S[4 * i4 + 2], k4.z * vj[tt]); acc = fmaf(r4.z, S[4 * i4 + 2], acc);
-              S[4 * i4 + 3] = fmaf(gamma, S[4 * i4 + 3], k4.w * vj[tt]); acc = fmaf(r4.w, S[4 * i4 + 3], acc);
-            }
+          for (int i4 = 0; i4 < DKQ / 4; ++i4) {
+            const float4 r4 = rr[i4], k4 = kk[i4], w4 = ww[i4];
+            acc0 = fmaf(r4.x, S[4 * i4 + 0], acc0); S[4 * i4 + 0] = fmaf(w4.x, S[4 * i4 + 0], k4.x * vj[tt]);
+            acc1 = fmaf(r4.y, S[4 * i4 + 1], acc1); S[4 * i4 + 1] = fmaf(w4.y, S[4 * i4 + 1], k4.y * vj[tt]);
+            acc0 = fmaf(r4.z, S[4 * i4 + 2], acc0); S[4 * i4 + 2] = fmaf(w4.z, S[4 * i4 + 2], k4.z * vj[tt]);
+            acc1 = fmaf(r4.w, S[4 * i4 + 3], acc1); S[4 * i4 + 3] = fmaf(w4.w, S[4 * i4 + 3], k4.w * vj[tt]);
           }
-          if (phase != 1) a.out[(int64_t)(s0 + tt) * ((int64_t)a.heads * dv) + (int64_t)hd * dv + j] = acc;
+          if (q == 0) acc0 = fmaf(sb[tt], vj[tt], acc0);          // the bonus, once
+        } else {
+#pragma unroll
+          for (int i4 = 0; i4 < DKQ / 4; ++i4) {
+            const float4 r4 = rr[i4], k4 = kk[i4];
+            S[4 * i4 + 0] = fmaf(gamma, S[4 * i4 + 0], k4.x * vj[tt]); acc0 = fmaf(r4.x, S[4 * i4 + 0], acc0);
+            S[4 * i4 + 1] = fmaf(gamma, S[4 * i4 + 1], k4.y * vj[tt]); acc1 = fmaf(r4.y, S[4 * i4 + 1], acc1);
+            S[4 * i4 + 2] = fmaf(gamma, S[4 * i4 + 2], k4.z * vj[tt]); acc0 = fmaf(r4.z, S[4 * i4 + 2], acc0);
+            S[4 * i4 + 3] = fmaf(gamma, S[4 * i4 + 3], k4.w * vj[tt]); acc1 = fmaf(r4.w, S[4 * i4 + 3], acc1);
+          }
         }
+        if (phase != 1) ls_acc[(tt * LS_Q + q) * dvr + j] = acc0 + acc1;
+      }
+    }
+    if (phase != 1) {
+      __syncthreads();
+      // the four parts of every output of the stage, summed in the order of the key channels
+      for (int idx = threadIdx.x; idx < n * dv; idx += blockDim.x) {
+        const int tt = idx / dv, jj = idx - tt * dv;
+        const float* pa = ls_acc + tt * LS_Q * dvr + jj;
+        a.out[(int64_t)(s0 + tt) * ((int64_t)a.heads * dv) + (int64_t)hd * dv + jj] =
+            ((pa[0] + pa[dvr]) + pa[2 * dvr]) + pa[3 * dvr];
       }
     }
   }
@@ -395,11 +413,11 @@ __global__ void __launch_bounds__(256) linear_scan_reg_kernel(ScanArgs a, int ph
     for (int i = threadIdx.x; i < DK; i += blockDim.x) ab[i] = sA[i];
     if (col) {
 #pragma unroll
-      for (int i = 0; i < DK; ++i) ab[DK + i * dv + j] = S[i];
+      for (int i = 0; i < DKQ; ++i) ab[DK + (i0 + i) * dv + j] = S[i];
     }
   } else if (hi == t1 && col) {
 #pragma unroll
-    for (int i = 0; i < DK; ++i) st[i * dv + j] = S[i];
+    for (int i = 0; i < DKQ; ++i) st[(i0 + i) * dv + j] = S[i];
   }
 }
 
@@ -520,8 +538,8 @@ extern "C" int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const voi
     return ERR_UNSUPPORTED;
   }
   void (*kernel)(ScanArgs, int) = mode == 0 ? linear_scan_kernel<0> : linear_scan_kernel<1>;
-  // key sizes of 16, 32, 64 and 128 with up to 256 values a head: the state in registers
-  bool regs = dv <= 256;
+  // key sizes of 16, 32, 64 and 128 with up to 128 values a head: the state in registers
+  bool regs = dv <= LS_MAX_DV;
   if (regs) {
     switch (dk) {
       case 16: kernel = mode == 0 ? linear_scan_reg_kernel<0, 16> : linear_scan_reg_kernel<1, 16>; break;
@@ -531,7 +549,8 @@ extern "C" int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const voi
       default: regs = false;
     }
   }
-  if (regs) smem = 0;
+  const int dvr = (dv + 31) / 32 * 32;
+  if (regs) smem = (size_t)LS_STAGE * LS_Q * dvr * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
@@ -545,7 +564,7 @@ extern "C" int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const voi
   a.state = state; a.slot_ids = slot_ids; a.row_start = row_start; a.out = out; a.ab = scratch;
   a.heads = heads; a.dk = dk; a.dv = dv; a.places = T / LS_CHUNK + B + 1;
   a.snap = scratch ? scratch + (size_t)a.places * heads * ((size_t)dk + (size_t)dk * dv) : nullptr;
-  const int threads = (dv + 31) / 32 * 32;
+  const int threads = regs ? LS_Q * dvr : dvr;
   if (ls_chunked(max_new)) {
     const int chunks = ceil_div(max_new, LS_CHUNK);
     if (scratch == nullptr || exl3_linear_scan_scratch_bytes(B, T, heads, dk, dv, max_new) > scratch_bytes ||
