@@ -158,6 +158,112 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qk_prep_kernel(QkPrepArgs a, in
   }
 }
 
+// The common case with 16-byte accesses: bfloat16 queries and cache, head sizes in multiples of 8 (no padding), pairs
+// of neighbouring features rotated (layout 1) or none, so that a pair lies inside the eight features that a lane holds.
+// A head takes LPH = 2, 4, ... 32 lanes (the power of two that covers hd / 8 and hdv / 8), so a warp works on 32 / LPH
+// heads side by side; block (t, y) takes the heads y * QP_WARPS * (32 / LPH) ... of token t.
+template <typename TX>
+__device__ inline void qp_load8(const TX* p, float (&v)[8]);
+template <>
+__device__ inline void qp_load8<float>(const float* p, float (&v)[8]) {
+  float a[4], b[4];
+  load_vec_cg(p, a);
+  load_vec_cg(p + 4, b);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { v[e] = a[e]; v[4 + e] = b[e]; }
+}
+template <>
+__device__ inline void qp_load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) { load_vec_cg(p, v); }
+
+template <typename TX, typename TS>
+__global__ void __launch_bounds__(QP_WARPS * 32) qk_prep_vec_kernel(QkPrepArgs a, int lph) {
+  __shared__ float s_sn[QP_TABLE], s_cs[QP_TABLE];
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = __ldcg(a.tok_pos + t);
+  const int pg = __ldcg(a.block_table + (int64_t)__ldcg(a.tok_seq + t) * a.bt_stride + pos / a.page);
+  const int in_page = pos % a.page;
+  const int half = a.rot >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cs;
+    rope_sincos((float)pos, a.f_hi[i], a.f_lo ? a.f_lo[i] : 0.0f, &sn, &cs);
+    s_sn[i] = sn * a.mscale;
+    s_cs[i] = cs * a.mscale;
+  }
+  __syncthreads();
+  const int per_warp = 32 / lph;
+  const int jobs = a.nh + 2 * a.nkv;
+  const int job = ((int)blockIdx.y * QP_WARPS + warp) * per_warp + lane / lph;
+  const int e0 = (lane % lph) * 8;
+  const bool live = job < jobs;
+  const bool is_q = job < a.nh, is_k = !is_q && job < a.nh + a.nkv;
+  const int head = is_q ? job : (is_k ? job - a.nh : job - a.nh - a.nkv);
+  const TX* x = static_cast<const TX*>(a.x) + (int64_t)t * a.ld;
+  __nv_bfloat16* kp = static_cast<__nv_bfloat16*>(a.k_pool);
+  __nv_bfloat16* vp = static_cast<__nv_bfloat16*>(a.v_pool);
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+  if (live && !is_q && !is_k) {
+    // a value head
+    if (e0 < a.hdv && pg >= 0) {
+      qp_load8<TX>(x + a.v_off + (int64_t)head * a.hdv + e0, v);
+      if (a.lambda != nullptr) {
+        const float lam = qp_load(a.lambda, a.lambda_dtype, 0);
+        float o[8];
+        qp_load8<TS>(static_cast<const TS*>(a.v_src) + (int64_t)t * a.v_src_ld + (int64_t)head * a.hdv + e0, o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = (1.0f - lam) * v[e] + lam * o[e];
+      }
+      store_vec(vp + (((int64_t)pg * a.nkv + head) * a.page + in_page) * a.hdv + e0, v);
+    }
+  }
+  const bool qk = live && (is_q || is_k);
+  const bool mine = qk && e0 < a.hd;
+  if (mine) qp_load8<TX>(x + (is_q ? a.q_off : a.k_off) + (int64_t)head * a.hd + e0, v);
+  float inv = 1.0f;
+  if (a.norm) {
+    // every lane takes part in the shuffles; a head's lanes are neighbours
+    float ss = 0.0f;
+    if (mine) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+    }
+    for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    inv = 1.0f / sqrtf(ss / (float)a.hd + a.eps);
+  }
+  if (!mine) return;
+  if (a.norm == 2) {
+    float w[8];
+    const float* wp = static_cast<const float*>(is_q ? a.q_w : a.k_w) + e0;
+    load_vec(wp, reinterpret_cast<float(&)[4]>(w[0]));
+    load_vec(wp + 4, reinterpret_cast<float(&)[4]>(w[4]));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= inv * w[e];
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= inv;
+  }
+  if (e0 < a.rot) {                                    // rot is a multiple of 8 here: all of the lane's pairs or none
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float sn = s_sn[(e0 >> 1) + p], cs = s_cs[(e0 >> 1) + p];
+      const float u = v[2 * p], w2 = v[2 * p + 1];
+      v[2 * p] = fmaf(u, cs, -w2 * sn);
+      v[2 * p + 1] = fmaf(w2, cs, u * sn);
+    }
+  }
+  if (is_q) {
+    store_vec(static_cast<__nv_bfloat16*>(a.q_out) + ((int64_t)t * a.nh + head) * a.hd + e0, v);
+  } else if (pg >= 0) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= a.k_mul;
+    store_vec(kp + (((int64_t)pg * a.nkv + head) * a.page + in_page) * a.hd + e0, v);
+  }
+}
+
 }  // namespace exl3
 
 using namespace exl3;
@@ -190,6 +296,27 @@ extern "C" int exl3_qk_prep(const void* x, int x_dtype, int64_t ld, int q_off, i
   a.tok_pos = tok_pos; a.tok_seq = tok_seq; a.block_table = block_table; a.bt_stride = bt_stride; a.page = page;
   a.q_out = q_out; a.q_out_dtype = q_out_dtype; a.k_out = k_out; a.k_out_dtype = k_out_dtype;
   a.k_pool = k_pool; a.v_pool = v_pool; a.pool_dtype = pool_dtype;
+  // the common case with 16-byte accesses (see qk_prep_vec_kernel)
+  const int widest = hd > a.hdv ? hd : a.hdv;
+  const bool src_ok = mix_lambda == nullptr || ((v_src_dtype == DT_BF16 || v_src_dtype == DT_F32) && v_src_ld % 8 == 0 &&
+                                                aligned16(v_src));
+  if (k_pool != nullptr && v_off >= 0 && pool_dtype == DT_BF16 && q_out_dtype == DT_BF16 && hd % 8 == 0 && hdv % 8 == 0 &&
+      hd_pad == hd && hdv_pad == hdv && widest <= 256 && ld % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 &&
+      v_off % 8 == 0 && (rot == 0 || (layout == 1 && rot % 8 == 0 && rot / 2 <= QP_TABLE)) &&
+      (norm != 2 || w_dtype == DT_F32) && (x_dtype == DT_BF16 || x_dtype == DT_F32) && aligned16(x) && aligned16(q_out) &&
+      aligned16(k_pool) && aligned16(v_pool) && src_ok && (norm != 2 || (aligned16(q_w) && aligned16(k_w)))) {
+    int lph = 1;
+    while (lph * 8 < widest) lph <<= 1;
+    const int per_block = QP_WARPS * (32 / lph);
+    const int jobs = nh + 2 * nkv;
+    const dim3 grid(T, ceil_div(jobs, per_block)), threads(QP_WARPS * 32);
+    const bool xf = x_dtype == DT_F32, sf = mix_lambda != nullptr && v_src_dtype == DT_F32;
+    if (xf && sf) launch_pdl(qk_prep_vec_kernel<float, float>, grid, threads, 0, stream, a, lph);
+    else if (xf) launch_pdl(qk_prep_vec_kernel<float, __nv_bfloat16>, grid, threads, 0, stream, a, lph);
+    else if (sf) launch_pdl(qk_prep_vec_kernel<__nv_bfloat16, float>, grid, threads, 0, stream, a, lph);
+    else launch_pdl(qk_prep_vec_kernel<__nv_bfloat16, __nv_bfloat16>, grid, threads, 0, stream, a, lph);
+    return launch_status("qk_prep");
+  }
   const size_t smem = (size_t)QP_WARPS * (hd > a.hdv ? hd : a.hdv) * sizeof(float);
   if (smem > 48 * 1024) { set_error("qk_prep: heads of %d features are too wide", hd); return ERR_UNSUPPORTED; }
   const int jobs = nh + nkv + (v_off >= 0 ? nkv : 0);

@@ -76,10 +76,13 @@ def rotate_ref(x, pos, f, factor, rot, interleaved):
 
 
 @pytest.mark.parametrize("dt", TYPES)
+@pytest.mark.parametrize("aligned", [False, True])
 @pytest.mark.parametrize("H, G, d, dv, norm, rot, layout, mix", [
     (4, 2, 24, 16, 2, 24, 1, True), (3, 1, 10, 6, 1, 0, 0, False), (6, 3, 16, 40, 2, 8, 1, False),
     (2, 2, 64, 128, 0, 32, 0, True), (5, 5, 10, 12, 2, 6, 1, True), (8, 1, 48, 48, 2, 48, 1, True)])
-def test_qk_prep_into_the_cache(dt, H, G, d, dv, norm, rot, layout, mix):
+def test_qk_prep_into_the_cache(dt, aligned, H, G, d, dv, norm, rot, layout, mix):
+    """``aligned``: offsets and pitches in multiples of 8, which the 16-byte form of the kernel takes where the head
+    sizes allow it; otherwise odd offsets, which only the general form takes."""
     g = torch.Generator().manual_seed(2)
     k_ = K()
     page, n_pages = 64, 6
@@ -87,21 +90,24 @@ def test_qk_prep_into_the_cache(dt, H, G, d, dv, norm, rot, layout, mix):
     rows = [(0, 60, 9), (1, 0, 3), (2, 130, 1)]
     tok_seq, tok_pos, row_start, slot_ids = step_layout(rows, g)
     T = int(row_start[-1])
-    off = 5
+    off = 8 if aligned else 5
     ld = off + (H + G) * d + G * dv + 3
+    if aligned:
+        ld = (ld + 7) // 8 * 8
+    so = 8 if aligned else 2                              # where the mixed-in values start in their rows
     x = torch.randn(T, ld, generator=g).to(dt).to(DEV)
     qw, kw = (1 + 0.3 * torch.randn(d, generator=g)).to(DEV), (1 + 0.3 * torch.randn(d, generator=g)).to(DEV)
     f = torch.tensor([100.0 ** (-2.0 * i / max(rot, 1)) for i in range(rot // 2)], dtype=torch.float64) * 0.37
     table = k_.rotary_table(f).to(DEV) if rot else None
     factor = 1.14
     lam = torch.tensor([0.35], device=DEV)
-    src = torch.randn(T, G * dv + 4, generator=g).to(dt).to(DEV)
+    src = torch.randn(T, (G * dv + 16 + 7) // 8 * 8, generator=g).to(dt).to(DEV)
     bt = torch.tensor([[4, 1, -1], [0, -1, -1], [3, 5, 2]], dtype=torch.int32, device=DEV)
     kp = torch.full((n_pages, G, page, dp), 7.0, dtype=dt, device=DEV)
     vp = torch.full((n_pages, G, page, dvp), 7.0, dtype=dt, device=DEV)
     q, none = k_.qk_prep(x, off, off + H * d, off + (H + G) * d, H, G, d, dv, dp, dvp, norm, qw if norm == 2 else None,
                          kw if norm == 2 else None, 1e-5, rot, layout, table, factor, 1.0,
-                         (lam, src[:, 2:2 + G * dv]) if mix else None, tok_pos, tok_seq, bt, page, dt, kp, vp)
+                         (lam, src[:, so:so + G * dv]) if mix else None, tok_pos, tok_seq, bt, page, dt, kp, vp)
     assert none is None
     xd = x.double().cpu()
     qr = xd[:, off:off + H * d].reshape(T, H, d)
@@ -118,7 +124,7 @@ def test_qk_prep_into_the_cache(dt, H, G, d, dv, norm, rot, layout, mix):
         qr = rotate_ref(qr, tok_pos.cpu(), f, factor, rot, layout == 1)
         kr = rotate_ref(kr, tok_pos.cpu(), f, factor, rot, layout == 1)
     if mix:
-        vr = 0.65 * vr + 0.35 * src[:, 2:2 + G * dv].double().cpu().reshape(T, G, dv)
+        vr = 0.65 * vr + 0.35 * src[:, so:so + G * dv].double().cpu().reshape(T, G, dv)
     want_q = torch.zeros(T, H, dp, dtype=torch.float64)
     want_q[..., :d] = qr
     close(q.reshape(T, H, dp), want_q, dt, "q")
