@@ -269,8 +269,9 @@ __global__ void linear_scan_kernel(ScanArgs a, int phase) {
 constexpr int LS_Q = 4;
 constexpr int LS_MAX_DV = 128;
 
-template <int MODE, int DK>
-__global__ void __launch_bounds__(LS_Q * LS_MAX_DV) linear_scan_reg_kernel(ScanArgs a, int phase) {
+template <int MODE, int DK, int PHASE>
+__global__ void __launch_bounds__(LS_Q * LS_MAX_DV) linear_scan_reg_kernel(ScanArgs a, int) {
+  constexpr int phase = PHASE;                       // 1 (a chunk's summary) needs neither r nor the outputs
   constexpr int DKQ = DK / LS_Q;
   __shared__ __align__(16) float sr[LS_STAGE * DK];
   __shared__ __align__(16) float sk[LS_STAGE * DK];
@@ -329,7 +330,7 @@ __global__ void __launch_bounds__(LS_Q * LS_MAX_DV) linear_scan_reg_kernel(ScanA
     for (int idx = threadIdx.x; idx < n * DK; idx += blockDim.x) {
       const int tt = idx / DK, i = idx - tt * DK;
       const int64_t t = s0 + tt;
-      sr[idx] = ls_load_act(a.r, a.rk_dtype, t * a.r_ld + (int64_t)hd * DK + i);
+      if (phase != 1) sr[idx] = ls_load_act(a.r, a.rk_dtype, t * a.r_ld + (int64_t)hd * DK + i);
       sk[idx] = ls_load_act(a.k, a.rk_dtype, t * a.k_ld + (int64_t)hd * DK + i);
       if (MODE == 0) {
         const float z = ls_load_act(a.wraw, a.w_dtype, t * a.w_ld + (int64_t)hd * DK + i) +
@@ -345,7 +346,7 @@ __global__ void __launch_bounds__(LS_Q * LS_MAX_DV) linear_scan_reg_kernel(ScanA
     __syncthreads();
     if (MODE == 0) {
       const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-      for (int tt = warp; tt < n; tt += nw) {
+      for (int tt = warp; phase != 1 && tt < n; tt += nw) {
         float acc = 0.0f;
         for (int i = lane; i < DK; i += 32)
           acc = fmaf(sr[tt * DK + i] * ls_load(a.u, a.wu_dtype, (int64_t)hd * DK + i), sk[tt * DK + i], acc);
@@ -377,20 +378,28 @@ __global__ void __launch_bounds__(LS_Q * LS_MAX_DV) linear_scan_reg_kernel(ScanA
 #pragma unroll
           for (int i4 = 0; i4 < DKQ / 4; ++i4) {
             const float4 r4 = rr[i4], k4 = kk[i4], w4 = ww[i4];
-            acc0 = fmaf(r4.x, S[4 * i4 + 0], acc0); S[4 * i4 + 0] = fmaf(w4.x, S[4 * i4 + 0], k4.x * vj[tt]);
-            acc1 = fmaf(r4.y, S[4 * i4 + 1], acc1); S[4 * i4 + 1] = fmaf(w4.y, S[4 * i4 + 1], k4.y * vj[tt]);
-            acc0 = fmaf(r4.z, S[4 * i4 + 2], acc0); S[4 * i4 + 2] = fmaf(w4.z, S[4 * i4 + 2], k4.z * vj[tt]);
-            acc1 = fmaf(r4.w, S[4 * i4 + 3], acc1); S[4 * i4 + 3] = fmaf(w4.w, S[4 * i4 + 3], k4.w * vj[tt]);
+            if (phase != 1) {
+              acc0 = fmaf(r4.x, S[4 * i4 + 0], acc0); acc1 = fmaf(r4.y, S[4 * i4 + 1], acc1);
+              acc0 = fmaf(r4.z, S[4 * i4 + 2], acc0); acc1 = fmaf(r4.w, S[4 * i4 + 3], acc1);
+            }
+            S[4 * i4 + 0] = fmaf(w4.x, S[4 * i4 + 0], k4.x * vj[tt]);
+            S[4 * i4 + 1] = fmaf(w4.y, S[4 * i4 + 1], k4.y * vj[tt]);
+            S[4 * i4 + 2] = fmaf(w4.z, S[4 * i4 + 2], k4.z * vj[tt]);
+            S[4 * i4 + 3] = fmaf(w4.w, S[4 * i4 + 3], k4.w * vj[tt]);
           }
           if (q == 0) acc0 = fmaf(sb[tt], vj[tt], acc0);          // the bonus, once
         } else {
 #pragma unroll
           for (int i4 = 0; i4 < DKQ / 4; ++i4) {
             const float4 r4 = rr[i4], k4 = kk[i4];
-            S[4 * i4 + 0] = fmaf(gamma, S[4 * i4 + 0], k4.x * vj[tt]); acc0 = fmaf(r4.x, S[4 * i4 + 0], acc0);
-            S[4 * i4 + 1] = fmaf(gamma, S[4 * i4 + 1], k4.y * vj[tt]); acc1 = fmaf(r4.y, S[4 * i4 + 1], acc1);
-            S[4 * i4 + 2] = fmaf(gamma, S[4 * i4 + 2], k4.z * vj[tt]); acc0 = fmaf(r4.z, S[4 * i4 + 2], acc0);
-            S[4 * i4 + 3] = fmaf(gamma, S[4 * i4 + 3], k4.w * vj[tt]); acc1 = fmaf(r4.w, S[4 * i4 + 3], acc1);
+            S[4 * i4 + 0] = fmaf(gamma, S[4 * i4 + 0], k4.x * vj[tt]);
+            S[4 * i4 + 1] = fmaf(gamma, S[4 * i4 + 1], k4.y * vj[tt]);
+            S[4 * i4 + 2] = fmaf(gamma, S[4 * i4 + 2], k4.z * vj[tt]);
+            S[4 * i4 + 3] = fmaf(gamma, S[4 * i4 + 3], k4.w * vj[tt]);
+            if (phase != 1) {
+              acc0 = fmaf(r4.x, S[4 * i4 + 0], acc0); acc1 = fmaf(r4.y, S[4 * i4 + 1], acc1);
+              acc0 = fmaf(r4.z, S[4 * i4 + 2], acc0); acc1 = fmaf(r4.w, S[4 * i4 + 3], acc1);
+            }
           }
         }
         if (phase != 1) ls_acc[(tt * LS_Q + q) * dvr + j] = acc0 + acc1;
@@ -540,15 +549,22 @@ extern "C" int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const voi
   void (*kernel)(ScanArgs, int) = mode == 0 ? linear_scan_kernel<0> : linear_scan_kernel<1>;
   // key sizes of 16, 32, 64 and 128 with up to 128 values a head: the state in registers
   bool regs = dv <= LS_MAX_DV;
+  void (*by_phase[3])(ScanArgs, int) = {kernel, kernel, kernel};
+#define EXL3_SCAN(DKV)                                                                                            \
+  case DKV:                                                                                                       \
+    for (int ph = 0; ph < 3; ++ph)                                                                                \
+      by_phase[ph] = mode == 0 ? (ph == 0 ? linear_scan_reg_kernel<0, DKV, 0> : ph == 1 ? linear_scan_reg_kernel<0, DKV, 1> \
+                                                                                         : linear_scan_reg_kernel<0, DKV, 2>) \
+                               : (ph == 0 ? linear_scan_reg_kernel<1, DKV, 0> : ph == 1 ? linear_scan_reg_kernel<1, DKV, 1> \
+                                                                                         : linear_scan_reg_kernel<1, DKV, 2>); \
+    break;
   if (regs) {
     switch (dk) {
-      case 16: kernel = mode == 0 ? linear_scan_reg_kernel<0, 16> : linear_scan_reg_kernel<1, 16>; break;
-      case 32: kernel = mode == 0 ? linear_scan_reg_kernel<0, 32> : linear_scan_reg_kernel<1, 32>; break;
-      case 64: kernel = mode == 0 ? linear_scan_reg_kernel<0, 64> : linear_scan_reg_kernel<1, 64>; break;
-      case 128: kernel = mode == 0 ? linear_scan_reg_kernel<0, 128> : linear_scan_reg_kernel<1, 128>; break;
+      EXL3_SCAN(16) EXL3_SCAN(32) EXL3_SCAN(64) EXL3_SCAN(128)
       default: regs = false;
     }
   }
+#undef EXL3_SCAN
   const int dvr = (dv + 31) / 32 * 32;
   if (regs) smem = (size_t)LS_STAGE * LS_Q * dvr * sizeof(float);
   if (smem > 48 * 1024) {
@@ -572,13 +588,13 @@ extern "C" int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const voi
       set_error("linear_scan: scratch of %zu bytes is too small for %d tokens", scratch_bytes, T);
       return ERR_SCRATCH;
     }
-    launch_pdl(kernel, dim3(heads, chunks, B), dim3(threads), smem, stream, a, 1);
+    launch_pdl(by_phase[1], dim3(heads, chunks, B), dim3(threads), smem, stream, a, 1);
     int rc = launch_status("linear_scan (chunks)");
     if (rc) return rc;
-    launch_pdl(kernel, dim3(heads, chunks, B), dim3(threads), smem, stream, a, 2);
+    launch_pdl(by_phase[2], dim3(heads, chunks, B), dim3(threads), smem, stream, a, 2);
     return launch_status("linear_scan (fold)");
   }
-  launch_pdl(kernel, dim3(heads, 1, B), dim3(threads), smem, stream, a, 0);
+  launch_pdl(by_phase[0], dim3(heads, 1, B), dim3(threads), smem, stream, a, 0);
   return launch_status("linear_scan");
 }
 
