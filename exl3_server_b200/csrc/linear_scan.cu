@@ -270,7 +270,7 @@ constexpr int LS_Q = 4;
 constexpr int LS_MAX_DV = 128;
 
 template <int MODE, int DK, int PHASE>
-__global__ void __launch_bounds__(LS_Q * LS_MAX_DV) linear_scan_reg_kernel(ScanArgs a, int) {
+__global__ void __launch_bounds__(LS_Q * LS_MAX_DV, DK <= 64 ? 2 : 1) linear_scan_reg_kernel(ScanArgs a, int) {
   constexpr int phase = PHASE;                       // 1 (a chunk's summary) needs neither r nor the outputs
   constexpr int DKQ = DK / LS_Q;
   __shared__ __align__(16) float sr[LS_STAGE * DK];
@@ -324,18 +324,36 @@ __global__ void __launch_bounds__(LS_Q * LS_MAX_DV) linear_scan_reg_kernel(ScanA
     }
   }
   const float gamma = MODE == 1 ? a.decay[hd] : 0.0f;
+  // A stage's r, k and decay inputs come into registers a stage ahead, so that their way from memory passes under the
+  // stage before's arithmetic instead of standing in front of the barrier (a block has at least 128 threads, so
+  // PER values a thread cover a stage).
+  constexpr int PER = LS_STAGE * DK / 128;
+  float pr[PER], pk[PER], pw[MODE == 0 ? PER : 1];
+  auto fetch = [&](int s0) {
+    const int n = min(LS_STAGE, hi - s0);
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+      const int idx = threadIdx.x + e * blockDim.x;
+      if (idx < n * DK) {
+        const int tt = idx / DK, i = idx - tt * DK;
+        const int64_t t = s0 + tt;
+        if (phase != 1) pr[e] = ls_load_act(a.r, a.rk_dtype, t * a.r_ld + (int64_t)hd * DK + i);
+        pk[e] = ls_load_act(a.k, a.rk_dtype, t * a.k_ld + (int64_t)hd * DK + i);
+        if (MODE == 0) pw[e] = ls_load_act(a.wraw, a.w_dtype, t * a.w_ld + (int64_t)hd * DK + i);
+      }
+    }
+  };
+  fetch(lo);
   for (int s0 = lo; s0 < hi; s0 += LS_STAGE) {
     const int n = min(LS_STAGE, hi - s0);
     __syncthreads();                                 // the stage before has been used, its outputs written
-    for (int idx = threadIdx.x; idx < n * DK; idx += blockDim.x) {
-      const int tt = idx / DK, i = idx - tt * DK;
-      const int64_t t = s0 + tt;
-      if (phase != 1) sr[idx] = ls_load_act(a.r, a.rk_dtype, t * a.r_ld + (int64_t)hd * DK + i);
-      sk[idx] = ls_load_act(a.k, a.rk_dtype, t * a.k_ld + (int64_t)hd * DK + i);
-      if (MODE == 0) {
-        const float z = ls_load_act(a.wraw, a.w_dtype, t * a.w_ld + (int64_t)hd * DK + i) +
-                        ls_load(a.w0, a.wu_dtype, (int64_t)hd * DK + i);
-        sw[idx] = expf(-expf(z));
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+      const int idx = threadIdx.x + e * blockDim.x;
+      if (idx < n * DK) {
+        if (phase != 1) sr[idx] = pr[e];
+        sk[idx] = pk[e];
+        if (MODE == 0) sw[idx] = expf(-expf(pw[e] + ls_load(a.w0, a.wu_dtype, (int64_t)hd * DK + idx % DK)));
       }
     }
     // the values of the stage's tokens, asked for before the barrier
@@ -344,6 +362,7 @@ __global__ void __launch_bounds__(LS_Q * LS_MAX_DV) linear_scan_reg_kernel(ScanA
     for (int tt = 0; tt < LS_STAGE; ++tt)
       vj[tt] = (col && tt < n) ? ls_load_act(a.v, a.v_dtype, (int64_t)(s0 + tt) * a.v_ld + (int64_t)hd * dv + j) : 0.0f;
     __syncthreads();
+    if (s0 + LS_STAGE < hi) fetch(s0 + LS_STAGE);
     if (MODE == 0) {
       const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
       for (int tt = warp; phase != 1 && tt < n; tt += nw) {
