@@ -135,10 +135,10 @@ def nikodra_config(z):
     from exl3_server_b200.config.nikodra import NikodraConfig, NikodraLayer
     hd = z["head_dim"]
     att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "v_mix": True,
-           "rot": {"base": 1000000.0, "dims": hd, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+           "rot": {"base": 500000.0, "dims": hd, "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     left = {k: att[k] for k in ("heads", "kv_heads", "dim", "vdim", "scale")}
     left["mask"] = {"size": 1024}
-    right = {"heads": z["heads"], "dim": 64, "vdim": hd, "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * i / z["heads"]) for i in range(z["heads"])],
+    right = {"heads": z["heads"], "dim": 64, "vdim": hd, "decay": [1.0 - 2.0 ** (-4.0 - 6.0 * i / z["heads"]) for i in range(z["heads"])],
              "rot": {"base": 10000.0, "dims": 64}}
     mlp = {"kind": "dense", "ff": z["ff"]}
     kinds = [("attention", att), ("attention", att), ("parallel", {"left": left, "right": right}),

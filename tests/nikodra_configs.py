@@ -52,8 +52,8 @@ CONFIGS = {
     ]),
     # heads of 64 and 128, a state of 64 x 128, blocks of exactly two pages, long decays
     "wide": NikodraConfig(vocab=300, width=128, norm_eps=1e-6, residual_mult=1.0, bigram=BIGRAM, layers=[
-        NikodraLayer("attention", attn(4, 2, 64, 128, 0.125, base=1000000.0, scaling=(4.0, 512, 32.0, 1.0), v_mix=True), dense(256)),
-        NikodraLayer("parallel", par(attn(2, 1, 128, 64, 0.09), 128, 2, 64, 128, (0.96875, 0.999), base=1000000.0), None),
+        NikodraLayer("attention", attn(4, 2, 64, 128, 0.125, base=250000.0, scaling=(2.0, 256, 24.0, 2.0), v_mix=True), dense(320)),
+        NikodraLayer("parallel", par(attn(2, 1, 128, 64, 0.09), 128, 2, 64, 128, (0.95, 0.998), base=250000.0), None),
         NikodraLayer("wkv", {"heads": 2, "dim": 64, "decay_rank": 16}, dense(192)),
         NikodraLayer("attention", attn(8, 2, 64, 128, 0.125, v_mix=True), None),
     ]),
@@ -62,7 +62,7 @@ CONFIGS = {
     "tensor": NikodraConfig(vocab=200, width=128, norm_eps=1e-6, residual_mult=0.5, bigram=BIGRAM, layers=[
         NikodraLayer("attention", attn(4, 2, 64, 64, 0.125, dims=32, scaling=(4.0, 256, 32.0, 1.0), v_mix=True), dense(128)),
         NikodraLayer("parallel", par(attn(4, 2, 128, 128, 0.09), 100, 2, 32, 32, (0.9, 0.99)), None),
-        NikodraLayer("attention", attn(8, 1, 128, 128, 0.09, base=1000000.0), None),
+        NikodraLayer("attention", attn(8, 1, 128, 128, 0.09, base=800000.0), None),
         NikodraLayer("attention", attn(6, 2, 64, 64, 0.125, v_mix=True), dense(96)),
     ]),
     # one mechanism alone

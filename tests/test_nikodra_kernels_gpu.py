@@ -36,7 +36,7 @@ def step_layout(rows, g):
 @pytest.mark.parametrize("dt", TYPES)
 def test_embed_hashed(dt):
     g = torch.Generator().manual_seed(1)
-    V, H, buckets, mp, mc = 50, 40, 11, 127, 17
+    V, H, buckets, mp, mc = 50, 40, 11, 131, 19
     table = torch.randn(V, H, generator=g).to(dt).to(DEV)
     extra = torch.randn(buckets + 1, H, generator=g).to(dt).to(DEV)
     rows = [(3, 0, 5), (0, 7, 1), (5, 2, 4), (1, 0, 1)]
@@ -79,7 +79,7 @@ def rotate_ref(x, pos, f, factor, rot, interleaved):
 @pytest.mark.parametrize("aligned", [False, True])
 @pytest.mark.parametrize("H, G, d, dv, norm, rot, layout, mix", [
     (4, 2, 24, 16, 2, 24, 1, True), (3, 1, 10, 6, 1, 0, 0, False), (6, 3, 16, 40, 2, 8, 1, False),
-    (2, 2, 64, 128, 0, 32, 0, True), (5, 5, 10, 12, 2, 6, 1, True), (8, 1, 48, 48, 2, 48, 1, True)])
+    (2, 2, 64, 128, 0, 32, 0, True), (5, 5, 10, 12, 2, 6, 1, True), (8, 1, 40, 40, 2, 40, 1, True)])
 def test_qk_prep_into_the_cache(dt, aligned, H, G, d, dv, norm, rot, layout, mix):
     """``aligned``: offsets and pitches in multiples of 8, which the 16-byte form of the kernel takes where the head
     sizes allow it; otherwise odd offsets, which only the general form takes."""
@@ -160,7 +160,7 @@ def test_qk_prep_without_a_cache_keeps_float32():
 @pytest.mark.parametrize("dt", TYPES)
 @pytest.mark.parametrize("H, G, d, dv, chunk, sink", [
     (4, 2, 24, 16, 0, True), (6, 2, 16, 40, 50, True), (2, 1, 128, 64, 128, True), (3, 1, 16, 8, 7, False),
-    (8, 2, 64, 128, 0, True), (4, 4, 48, 48, 200, True), (5, 5, 16, 16, 0, False)])
+    (8, 2, 64, 128, 0, True), (4, 4, 40, 40, 150, True), (5, 5, 16, 16, 0, False)])
 def test_attention_with_sink_blocks_and_values_of_another_width(dt, H, G, d, dv, chunk, sink):
     g = torch.Generator().manual_seed(4)
     k_ = K()
